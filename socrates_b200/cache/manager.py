@@ -35,11 +35,13 @@ from .allocator import OutOfPages, PageAllocator, pages_for
 @dataclass(frozen=True)
 class PagedKVSpec:
     """Keys and values of `num_kv_heads` heads; keys have `head_dim` dims, values
-    `v_head_dim` (None: the same); `window` keys are kept (None: all of them)."""
+    `v_head_dim` (None: the same); `window` keys are kept (None: all of them), and beside
+    the window the first `keep_first` keys of the sequence."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    keep_first: int = 0
 
     @property
     def value_dim(self) -> int:
@@ -97,6 +99,19 @@ class PageGroup:
         if self.spec.window is None:
             return 0
         return max(0, next_pos - self.spec.window + 1) // self.page_size
+
+    def kept_blocks(self) -> int:
+        """Logical blocks at the start of a row that a windowed group never gives back: those that
+        hold one of the first `keep_first` keys."""
+        if self.spec.window is None:
+            return 0
+        return pages_for(self.spec.keep_first, self.page_size)
+
+    def lacking(self, row: int, length: int, last: int) -> List[int]:
+        """The logical blocks below `last` that a row of `length` tokens does not hold yet and that a
+        query at `length` or later can see: inside the window, or among the kept first blocks."""
+        first, kept = self.first_needed_block(length), self.kept_blocks()
+        return [b for b in range(len(self.row_pages[row]), last) if b >= first or b < kept]
 
     def owned(self, row: int) -> List[int]:
         return [p for p in self.row_pages[row] if p != 0]
@@ -180,11 +195,7 @@ class CacheManager:
         the first block a later query can still see.
         """
         last = pages_for(new_len, self.page_size)              # exclusive
-        out = []
-        for g in self.groups:
-            first = g.first_needed_block(self.lengths[row])
-            out.append(max(0, last - max(first, len(g.row_pages[row]))))
-        return out
+        return [len(g.lacking(row, self.lengths[row], last)) for g in self.groups]
 
     def can_reserve(self, row: int, new_len: int) -> bool:
         if new_len > self.max_len:
@@ -209,13 +220,13 @@ class CacheManager:
             if need == 0:
                 continue
             have = g.row_pages[row]
-            first = g.first_needed_block(self.lengths[row])
-            while len(have) < min(first, last):                 # blocks no query will see again
-                have.append(0)
+            blocks = g.lacking(row, self.lengths[row], last)
             pages = g.allocator.alloc(need)
-            start = len(have)
-            have.extend(pages)
-            g.host_table[row, start:start + need] = torch.tensor(pages, dtype=torch.int32)
+            for b, page in zip(blocks, pages):
+                while len(have) < b:                            # blocks no query will see again
+                    have.append(0)
+                have.append(page)
+                g.host_table[row, b] = page
             g.dirty.add(row)
         return True
 
@@ -230,7 +241,7 @@ class CacheManager:
             keep_from = g.first_needed_block(new_len)
             have = g.row_pages[row]
             upto = min(keep_from, len(have))
-            gone = [b for b in range(g.freed_upto[row], upto) if have[b] != 0]
+            gone = [b for b in range(max(g.freed_upto[row], g.kept_blocks()), upto) if have[b] != 0]
             g.freed_upto[row] = max(g.freed_upto[row], upto)
             if gone:
                 g.allocator.free([have[b] for b in gone])

@@ -14,6 +14,7 @@ from typing import Any, Dict, Mapping
 from .bofusun import BofusunConfig
 from .loletar import LoletarConfig
 from .qwen3 import ConfigError, Qwen3Config
+from .samerax import SameraxConfig
 
 _ARCHITECTURES: Dict[str, Any] = {}
 
@@ -59,3 +60,4 @@ def load_config(model_dir: str | Path):
 register_architecture(Qwen3Config.architecture, Qwen3Config)
 register_architecture(BofusunConfig.architecture, BofusunConfig)
 register_architecture(LoletarConfig.architecture, LoletarConfig)
+register_architecture(SameraxConfig.architecture, SameraxConfig)

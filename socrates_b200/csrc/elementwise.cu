@@ -253,6 +253,10 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
 // row of the input may be wider than the heads (`row_width`): other columns of the same product.
 // The input is either qkv in the model dtype, or (parts != null) S float32 partial sums
 // of a split-K product, added here in the order s = 0, 1, ...
+// `bias` (float32, one entry per input column, or null) is added to the input first.  A query or
+// key head may hold several maps of `sub` dims each (sub divides D): every map rotates its own
+// first R dims.  `magnitude` multiplies every cosine and sine (an encoding that also scales the
+// rotated dims); dims that do not rotate are not scaled.
 template <typename T>
 __global__ void qk_norm_rope_kvwrite_kernel(
     const T* __restrict__ qkv, const float* __restrict__ parts, int S, size_t part_stride,
@@ -260,7 +264,8 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     const float* __restrict__ q_gain, const float* __restrict__ k_gain,
     const float* __restrict__ inv_freq, int R, const int* __restrict__ positions,
     const int* __restrict__ token_rows, const int* __restrict__ block_table, int table_width,
-    int BS, float eps, int Hq, int Hkv, int D, int write_kv, int Dv, int row_width, int neighbours) {
+    int BS, float eps, int Hq, int Hkv, int D, int write_kv, int Dv, int row_width, int neighbours,
+    const float* __restrict__ bias, int sub, float magnitude) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     __shared__ float buf[4][256];
@@ -288,6 +293,7 @@ __global__ void qk_norm_rope_kvwrite_kernel(
         } else {
             v = to_float(qkv[base + i]);
         }
+        if (bias != nullptr) v += bias[base - (size_t)n * row_width + i];
         y[i] = v;
         ss += v * v;
     }
@@ -313,13 +319,14 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     const int half = R >> 1;
     for (int i = lane; i < Dh; i += 32) {
         float o = y[i];
-        if (!is_v && i < R) {
+        const int ii = i % sub;          // a head of several maps: every `sub` dims rotate on their own
+        if (!is_v && ii < R) {
             // the partner of dim i and the frequency they share: halves (j, j + R/2) or neighbours (2j, 2j+1)
-            const bool first = neighbours ? (i & 1) == 0 : i < half;
-            const int j = neighbours ? i >> 1 : (first ? i : i - half);
+            const bool first = neighbours ? (ii & 1) == 0 : ii < half;
+            const int j = neighbours ? ii >> 1 : (first ? ii : ii - half);
             const int mate = neighbours ? (i ^ 1) : (first ? i + half : i - half);
             const float ang = (float)pos * inv_freq[j];
-            const float c = cosf(ang), s = sinf(ang);
+            const float c = cosf(ang) * magnitude, s = sinf(ang) * magnitude;
             o = first ? y[i] * c - y[mate] * s : y[i] * c + y[mate] * s;
         }
         dst[i] = from_float<T>(o);
@@ -548,10 +555,12 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
                       void* v_pool, const float* q_gain, const float* k_gain, const float* inv_freq,
                       int rotary_dim, const int* positions, const int* token_rows, const int* block_table,
                       int table_width, int page_size, float eps, int Hq, int Hkv, int D, int N, int write_kv,
-                      int Dv, int row_width, int neighbours, cudaStream_t stream) {
+                      int Dv, int row_width, int neighbours, const float* bias, int sub, float magnitude,
+                      cudaStream_t stream) {
     const int n_heads = Hq + 2 * Hkv;
     const bool fast = (rotary_dim == D || rotary_dim == 0) && (D == 64 || D == 128 || D == 256) && Dv == D &&
-                      row_width == n_heads * D && !(neighbours && rotary_dim > 0);
+                      row_width == n_heads * D && !(neighbours && rotary_dim > 0) && bias == nullptr && sub == D &&
+                      magnitude == 1.0f;
     // Heads per block: 4 (a head per warp) while that still fills the GPU, more for long batches.
     int hpb = 4;
     if (fast) {
@@ -576,7 +585,7 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
     else if (fast) { SB_QK_FAST(8) }
 #undef SB_QK_FAST
     else sb::launch(qk_norm_rope_kvwrite_kernel<T>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, D, write_kv, Dv,
-                    row_width, neighbours);
+                    row_width, neighbours, bias, sub, magnitude);
 #undef SB_QK_ARGS
 }
 
@@ -589,7 +598,10 @@ extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, const float* parts, int 
                                        const int* token_rows, const int* block_table, int table_width,
                                        int page_size, float eps, int Hq, int Hkv, int D, int N,
                                        int write_kv, int dtype, int Dv, int row_width, int neighbours,
-                                       cudaStream_t stream) {
+                                       const float* bias, int sub, float magnitude, cudaStream_t stream) {
+    if (sub <= 0) sub = D;
+    SB_REQUIRE(D % sub == 0 && rotary_dim <= sub, "qk_norm_rope: heads of %d dims do not hold maps of %d with %d rotating",
+               D, sub, rotary_dim);
     SB_REQUIRE(Dv > 0 && Dv <= 256, "qk_norm_rope: value head size %d is outside 1..256", Dv);
     SB_REQUIRE(row_width >= Hq * D + (write_kv ? Hkv * (D + Dv) : 0),
                "qk_norm_rope: rows of %d columns do not hold the heads", row_width);
@@ -605,11 +617,11 @@ extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, const float* parts, int 
     if (dtype == SB_F32)
         qk_launch<float>(qkv, parts, S, (size_t)part_stride, q_out, k_pool, v_pool, q_gain, k_gain, inv_freq,
                          rotary_dim, positions, token_rows, block_table, table_width, page_size, eps, Hq, Hkv, D, N,
-                         write_kv, Dv, row_width, neighbours, stream);
+                         write_kv, Dv, row_width, neighbours, bias, sub, magnitude, stream);
     else if (dtype == SB_BF16)
         qk_launch<__nv_bfloat16>(qkv, parts, S, (size_t)part_stride, q_out, k_pool, v_pool, q_gain, k_gain,
                                  inv_freq, rotary_dim, positions, token_rows, block_table, table_width, page_size,
-                                 eps, Hq, Hkv, D, N, write_kv, Dv, row_width, neighbours, stream);
+                                 eps, Hq, Hkv, D, N, write_kv, Dv, row_width, neighbours, bias, sub, magnitude, stream);
     else
         SB_REQUIRE(false, "qk_norm_rope: unknown dtype %d", dtype);
     SB_LAUNCH_CHECK();
@@ -710,5 +722,24 @@ extern "C" int sb_silu_mul(void* out, const void* gate_up, int N, int F, int int
             (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, total, F, interleaved);
     else
         SB_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
+    SB_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
+// Capped logits: x <- cap * tanh(x / cap), float32, in place.
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    const float inv = 1.0f / cap;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
+}
+
+extern "C" int sb_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+    SB_REQUIRE(total >= 0 && cap > 0.f, "softcap: %lld values capped at %f", total, (double)cap);
+    if (total == 0) return 0;
+    size_t blocks = ((size_t)total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    sb::launch(softcap_kernel, dim3((int)blocks), dim3(256), 0, stream, x, (size_t)total, cap);
     SB_LAUNCH_CHECK();
 }

@@ -205,7 +205,37 @@ __global__ void __launch_bounds__(256) moe_passthrough_kernel(float* __restrict_
     for (int i = threadIdx.x; i < d; i += blockDim.x) slab[(size_t)n * d + i] = w * to_float(x[(size_t)n * d + i]);
 }
 
+// Routing by a table: token id t uses the experts table[t, 0..top-1] (distinct), each with weight 1 / top.
+// Writes the dense weights [N, E] (zero where not chosen) that the scaling kernel reads.  A negative id -1 - j
+// stands for feedback[j], a token that an earlier kernel on the stream wrote (as in the embedding).
+__global__ void __launch_bounds__(128) moe_table_kernel(float* __restrict__ weights, const int* __restrict__ ids,
+                                                        const int* __restrict__ feedback, const int* __restrict__ table,
+                                                        int N, int E, int top, int V) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    int id = ids[n];
+    if (id < 0 && feedback != nullptr) id = feedback[-1 - id];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const int* row = table + (size_t)id * top;
+    const float share = 1.0f / (float)top;
+    for (int e = lane; e < E; e += 32) {
+        float w = 0.f;
+        for (int j = 0; j < top; ++j) w = row[j] == e ? share : w;
+        weights[(size_t)n * E + e] = w;
+    }
+}
+
 }  // namespace
+
+extern "C" int sb_moe_table(float* weights, const int* ids, const int* feedback, const int* table, int N, int E,
+                            int top, int V, cudaStream_t stream) {
+    SB_REQUIRE(N >= 0 && E > 0 && top >= 1 && top <= E && V > 0, "moe_table: bad sizes N=%d E=%d top=%d V=%d", N, E, top, V);
+    if (N == 0) return 0;
+    sb::launch(moe_table_kernel, dim3((N + 3) / 4), dim3(128), 0, stream, weights, ids, feedback, table, N, E, top, V);
+    SB_LAUNCH_CHECK();
+}
 
 extern "C" int sb_moe_route(const float* logits, const float* correction, float* weights, int* ids, float* picked,
                             int N, int E, int groups, int keep, int top, cudaStream_t stream) {

@@ -134,8 +134,8 @@ class Scheduler:
             need = pages_for(total, self.cache.page_size)
             if g.spec.window is not None:
                 # a windowed group holds the window and the token being written, which may
-                # straddle one page edge more than their count fills
-                need = min(need, pages_for(g.spec.window + 1, self.cache.page_size) + 1)
+                # straddle one page edge more than their count fills, and the first blocks it keeps
+                need = min(need, pages_for(g.spec.window + 1, self.cache.page_size) + 1 + g.kept_blocks())
             if need > g.allocator.num_pages:
                 raise TooLong(f"{total} tokens need {need} pages at once; the pool has {g.allocator.num_pages}")
         req.sampling.validate()

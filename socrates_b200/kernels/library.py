@@ -30,7 +30,7 @@ _SIGNATURES = {
     "sb_set_dependent_launch": [I],
     "sb_embed": [P, P, P, I, I, I, I, P, F, P],
     "sb_add_rmsnorm": [P, P, I, LL, P, P, P, I, I, F, I, P],
-    "sb_qk_norm_rope_kvwrite": [P, P, I, LL, P, P, P, P, P, P, I, P, P, P, I, I, F, I, I, I, I, I, I, I, I, I, P],
+    "sb_qk_norm_rope_kvwrite": [P, P, I, LL, P, P, P, P, P, P, I, P, P, P, I, I, F, I, I, I, I, I, I, I, I, I, P, I, F, P],
     "sb_silu_mul": [P, P, I, I, I, I, P],
     "sb_sample": [P, P, P, P, P, I, I, P, P],
     "sb_sample_slices": [I],
@@ -64,6 +64,11 @@ _SIGNATURES = {
     "sb_moe_scale": [P, P, I, I, I, I, I, P],
     "sb_moe_passthrough": [P, P, P, I, I, I, I, I, P],
     "sb_attention_bias_tile": [P, P, P, P, P, I, P, P, P, I, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, I, I, F, P],
+    "sb_softcap": [P, LL, F, P],
+    "sb_moe_table": [P, P, P, P, I, I, I, I, P],
+    "sb_attention_diff": [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, F, F, F, I, P, P, I, P],
+    "sb_attention_diff_tile_supports": [I, I, I, I, I],
+    "sb_attention_diff_tile": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, F, I, P],
     "sb_attention_bias": [P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P, P, I, I, I, F, P],
 }
 

@@ -124,7 +124,8 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
                          positions: torch.Tensor, token_rows: torch.Tensor, block_table: torch.Tensor,
                          eps: float, num_heads: int, num_kv_heads: int, head_dim: int,
                          value_dim: Optional[int] = None, row_width: Optional[int] = None,
-                         neighbours: bool = False) -> None:
+                         neighbours: bool = False, bias: Optional[torch.Tensor] = None,
+                         map_dim: Optional[int] = None, magnitude: float = 1.0) -> None:
     """Per-head norm, rotation and paged KV write for N tokens.
 
     qkv [N, (Hq+2Hkv)*D] in the model dtype, or float32 [S, N, (Hq+2Hkv)*D] partial sums
@@ -133,7 +134,9 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
     `value_dim`: value heads of another size Dv (v_pool [pages, Hkv, BS, Dv]); `row_width`: the
     rows of qkv are wider than the heads (more columns of the same product follow them; without
     pools only the Hq query heads need be there); `neighbours`: dim 2j rotates with dim 2j+1
-    instead of dim j with dim j + rotary_dim/2.
+    instead of dim j with dim j + rotary_dim/2.  `bias`: float32 [row_width], added to the input
+    columns first.  `map_dim`: a query or key head holds head_dim / map_dim maps, each of which
+    rotates its own first rotary_dim dims.  `magnitude` multiplies every cosine and sine.
     """
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     Dv = D if value_dim is None else int(value_dim)
@@ -162,13 +165,18 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
     for g, nm in ((q_gain, "q_gain"), (k_gain, "k_gain")):
         if g is not None:
             _want(g, nm, torch.float32, (D,))
+    if bias is not None:
+        _want(bias, "bias", torch.float32, (width,))
+    sub = D if map_dim is None else int(map_dim)
+    if sub < 1 or D % sub or rotary_dim > sub:
+        raise KernelError(f"heads of {D} dims do not hold maps of {sub} dims with {rotary_dim} rotating")
     lib = library()
     check(lib, lib.sb_qk_norm_rope_kvwrite(
         None if parts else _ptr(qkv), _ptr(qkv) if parts else None, qkv.shape[0] if parts else 0,
         N * width, _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq),
         rotary_dim, _ptr(positions), _ptr(token_rows), _ptr(block_table), block_table.shape[1],
         page_size, float(eps), Hq, Hkv, D, N, int(write_kv), _code(q_out.dtype), Dv, width, int(neighbours),
-        _stream()), "qk_norm_rope_kvwrite")
+        _ptr(bias), sub, float(magnitude), _stream()), "qk_norm_rope_kvwrite")
 
 
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, interleaved: bool = False) -> None:
@@ -934,3 +942,98 @@ def moe_passthrough(slab: torch.Tensor, x: torch.Tensor, weights: torch.Tensor, 
     lib = library()
     check(lib, lib.sb_moe_passthrough(_ptr(slab), _ptr(x), _ptr(weights), N, weights.shape[1], int(first_identity), d,
                                       _code(x.dtype), _stream()), "moe_passthrough")
+
+
+def moe_table(weights: torch.Tensor, ids: torch.Tensor, table: torch.Tensor,
+              feedback: Optional[torch.Tensor] = None) -> None:
+    """Routing by a table: weights[n, e] = 1 / top if e is among table[ids[n], :], else 0.  weights float32
+    [N, E]; ids int32 [N] (an id -1 - j stands for feedback[j], as in `embed`); table int32 [V, top]."""
+    N, E = weights.shape
+    _want(weights, "weights", torch.float32)
+    _want(ids, "ids", torch.int32, (N,))
+    _want(table, "table", torch.int32)
+    if table.dim() != 2 or not 1 <= table.shape[1] <= E:
+        raise KernelError(f"table must be [vocab, 1..{E}], got {tuple(table.shape)}")
+    if feedback is not None:
+        _want(feedback, "feedback", torch.int32)
+    lib = library()
+    check(lib, lib.sb_moe_table(_ptr(weights), _ptr(ids), _ptr(feedback), _ptr(table), N, E, table.shape[1],
+                                table.shape[0], _stream()), "moe_table")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place; x float32."""
+    _want(x, "x", torch.float32)
+    lib = library()
+    check(lib, lib.sb_softcap(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+
+
+# Differential attention: two score maps per head over one set of values.
+
+def _diff_shapes(out, q, k_pool, v_pool, num_heads):
+    N = q.shape[0]
+    pages, Hkv, BS, Dk2 = k_pool.shape
+    if Dk2 % 2:
+        raise KernelError(f"key rows of {Dk2} dims do not hold two maps")
+    dim, Dv = Dk2 // 2, v_pool.shape[3]
+    _want(q, "q", k_pool.dtype, (N, num_heads * 2 * dim))
+    _want(out, "out", q.dtype, (N, num_heads * Dv))
+    _want(k_pool, "k_pool")
+    _want(v_pool, "v_pool", k_pool.dtype, (pages, Hkv, BS, Dv))
+    return N, Hkv, BS, dim, Dv
+
+
+def attention_diff(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                   block_table: torch.Tensor, token_rows: torch.Tensor, positions: torch.Tensor, num_heads: int,
+                   scale: float, lam: float, eps: float, out_scale: float, window: int = 0, keep_first: int = 0,
+                   num_partitions: int = 1, part_o: Optional[torch.Tensor] = None,
+                   part_ml: Optional[torch.Tensor] = None) -> None:
+    """Paged causal differential attention, one query per token.  q [N, H*2*dim] holds per head [map 1 | map 2],
+    k_pool [pages, Hkv, BS, 2*dim] likewise, v_pool [pages, Hkv, BS, Dv], out [N, H*Dv]:
+    o = softmax(s1) v - lam * softmax(s2) v, then o / sqrt(mean(o^2) + eps) * out_scale per head.  Query i sees
+    key j <= i if i - j < window or j < keep_first (window 0: every key).  All arithmetic is float32.
+    With `num_partitions` > 1 the visible keys are cut into equal shares, one block each, merged by a second
+    kernel through the float32 scratch part_o (N*H*2*NP*Dv) and part_ml (N*H*2*NP*2)."""
+    N, Hkv, BS, dim, Dv = _diff_shapes(out, q, k_pool, v_pool, num_heads)
+    _want(block_table, "block_table", torch.int32)
+    _want(token_rows, "token_rows", torch.int32, (N,))
+    _want(positions, "positions", torch.int32, (N,))
+    if num_partitions > 1:
+        _want(part_o, "part_o", torch.float32)
+        _want(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < N * num_heads * 2 * num_partitions * Dv or part_ml.numel() < N * num_heads * 4 * num_partitions:
+            raise KernelError("attention scratch buffers are too small")
+    lib = library()
+    check(lib, lib.sb_attention_diff(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                     block_table.shape[1], _ptr(token_rows), _ptr(positions), N, num_heads, Hkv, dim, Dv,
+                                     BS, int(window), int(keep_first), float(scale), float(lam), float(eps),
+                                     float(out_scale), int(num_partitions), _ptr(part_o), _ptr(part_ml), _code(q.dtype),
+                                     _stream()), "attention_diff", kernels=2 if num_partitions > 1 else 1)
+
+
+def attention_diff_tile_supports(num_heads: int, num_kv_heads: int, map_dim: int, value_dim: int,
+                                 dtype: torch.dtype) -> bool:
+    """Whether the tile kernel for prompt portions takes this shape (maps whose rows are whole 16-byte pieces,
+    up to 128 dims; value heads up to 128 dims)."""
+    return bool(library().sb_attention_diff_tile_supports(num_heads, num_kv_heads, map_dim, value_dim, _code(dtype)))
+
+
+def attention_diff_tile(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                        block_table: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor,
+                        seq_first_pos: torch.Tensor, num_heads: int, scale: float, lam: float, eps: float,
+                        out_scale: float, window: int = 0, keep_first: int = 0) -> None:
+    """`attention_diff` for prompt portions: request r brings tokens seq_starts[r] .. seq_starts[r+1]-1 at
+    positions seq_first_pos[r], +1, ... of cache row seq_rows[r]; a block serves a tile of consecutive tokens of
+    one request.  The same arithmetic in float32."""
+    N, Hkv, BS, dim, Dv = _diff_shapes(out, q, k_pool, v_pool, num_heads)
+    R = seq_rows.numel()
+    _want(block_table, "block_table", torch.int32)
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    _want(seq_first_pos, "seq_first_pos", torch.int32, (R,))
+    lib = library()
+    check(lib, lib.sb_attention_diff_tile(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                          block_table.shape[1], _ptr(seq_starts), _ptr(seq_rows), _ptr(seq_first_pos),
+                                          R, N, num_heads, Hkv, dim, Dv, BS, int(window), int(keep_first), float(scale),
+                                          float(lam), float(eps), float(out_scale), _code(q.dtype), _stream()),
+          "attention_diff_tile")

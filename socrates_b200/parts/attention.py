@@ -172,7 +172,7 @@ class GQAAttention(Part):
         ops.qk_norm_rope_kvwrite(
             qkv, q, k_pool if cache.writes else None, v_pool if cache.writes else None,
             self.q_gain, self.k_gain, inv_freq, rotary_dim, ctx.positions, ctx.token_rows, table,
-            eps, self.Hq, self.Hkv, self.D)
+            eps, self.Hq, self.Hkv, self.D, magnitude=getattr(self.position, "magnitude", 1.0))
         attn = ctx.buffers.take("attn", N, (self.Hq * self.D,), ctx.dtype)
         paged_attention(ctx, attn, q, k_pool, v_pool, table, self.Hq, self.scale, self.window or 0,
                         cache.manager.max_len)

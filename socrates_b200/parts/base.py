@@ -44,7 +44,8 @@ class ParamSpec:
     role "gain":   a norm gain (or another small float32 parameter), always held as float32 on the device.
     role "int":    an integer table, int32 on the device.
     init "normal": N(0, 0.02); init "gain": 1 + N(0, 0.1); init "around_zero": N(0, 0.1);
-    init "uniform": U(lo, hi) with `bounds` = (lo, hi).
+    init "uniform": U(lo, hi) with `bounds` = (lo, hi); init "distinct" (role "int"): every row holds
+    different integers from lo .. hi - 1.
     """
     shape: Tuple[int, ...]
     role: str = "matrix"

@@ -62,6 +62,31 @@ class PreNormBlock:
 register_part("arrangement", "pre_norm", lambda layer_spec, name="": PreNormBlock(layer_spec))
 
 
+class PreNormMixerBlock(PreNormBlock):
+    """A pre-norm layer without a feed-forward: x = x + mixer(norm_0(x))."""
+
+    def __init__(self, layer_spec):
+        if len(layer_spec.norms) != 1 or layer_spec.feed_forward is not None:
+            raise ValueError("a pre_norm_mixer block has one norm and no feed-forward")
+        pre = layer_spec.prefix
+        self.norms = [build_part("norm", s, pre + s.name) for s in layer_spec.norms]
+        self.mixer = build_part("mixer", layer_spec.mixer, pre + layer_spec.mixer.name)
+        self.feed_forward = None
+
+    def parts(self):
+        return [*self.norms, self.mixer]
+
+    def streamed_weights(self):
+        return [*getattr(self.mixer, "streamed_weights", list)()]
+
+    def forward(self, ctx, stream: ResidualStream, cache) -> None:
+        h = self.norms[0].apply(ctx, stream)
+        stream.pending = self.mixer.forward(ctx, h, cache)
+
+
+register_part("arrangement", "pre_norm_mixer", lambda layer_spec, name="": PreNormMixerBlock(layer_spec))
+
+
 class SandwichBlock:
     """A block that norms every branch on both sides:
     x = x + norm_1b(mixer(norm_1(x))); x = x + norm_2b(feed_forward(norm_2(x))).

@@ -3,7 +3,7 @@
 Embedding: x = table[ids] (model/qwen/qwen_kv_paged.py:198,219), widened to the
 float32 residual and multiplied by `scale` where the plan gives one.  Head: logits = x W^T with W the embedding table when the
 configuration ties them (:224) or `lm_head.weight` otherwise; only the rows whose
-logits were asked for are computed, in float32.
+logits were asked for are computed, in float32; with `softcap` c they become c * tanh(logits / c).
 """
 
 from __future__ import annotations
@@ -45,6 +45,10 @@ class LMHead(Part):
         self.hidden = int(spec.params["hidden_size"])
         self.tied_to: Optional[str] = spec.params.get("tied_to")
         self.tensor = self.name + str(spec.params.get("suffix", "weight"))
+        cap = spec.params.get("softcap")                      # logits <- cap * tanh(logits / cap)
+        self.softcap: Optional[float] = float(cap) if cap else None
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"a logit cap of {self.softcap}")
         self.linear: Optional[Linear] = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
@@ -63,7 +67,10 @@ class LMHead(Part):
         return [self.linear.weight]
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        return self.linear(ctx, x, "logits", out="wanted_float32")
+        logits = self.linear(ctx, x, "logits", out="wanted_float32")
+        if self.softcap is not None:
+            ops.softcap(logits, self.softcap)
+        return logits
 
 
 register_part("embedding", "embedding", Embedding)

@@ -40,6 +40,8 @@ class Retention(Part):
         self.eps = float(p["norm_eps"])
         self.key_scale = float(p.get("key_scale", self.dk ** -0.5))
         self.position = build_part("position", p["position"], "")
+        if getattr(self.position, "magnitude", 1.0) != 1.0:
+            raise ValueError("the retention kernel rotates with plain cosines and sines; a scaled encoding is not served")
         self.qkvg: Optional[Linear] = None
         self.o: Optional[Linear] = None
         self.decay_t: Optional[torch.Tensor] = None

@@ -9,6 +9,9 @@
 The weights are the plain scores (without the correction, not renormalized).  The router's product
 and the choice are float32 in both engines.
 
+With `router: "table"` there is no router product at all: an integer table [vocab, top] names the experts of
+every token ID (no expert twice in a row), and each of them counts 1 / top.
+
 How it runs: all experts' gate/up matrices are one matrix [E * 2F, d] (rows interleaved as in the dense
 gated feed-forward, so the product's epilogue applies silu(gate) * up) and all down matrices one matrix
 [d, E * F].  The routing kernel leaves a dense float32 weight per (token, expert), zero where the expert
@@ -18,7 +21,7 @@ the branch's partial sums.  Nothing is read back and no shape depends on the cho
 recorded into graphs like any other; the price is that every expert is computed for every token, which
 costs nothing while a step streams the weights anyway (decoding) and E / top times the needed products
 for long prompt portions.
-Tensors: `<name>router`, `correction`, `e<i>.gate`, `e<i>.up`, `e<i>.down`.
+Tensors: `<name>router`, `correction` (or `table`), `e<i>.gate`, `e<i>.up`, `e<i>.down`.
 """
 
 from __future__ import annotations
@@ -51,6 +54,12 @@ class RoutedFeedForward(Part):
         self.groups = int(p.get("groups", 1))
         self.keep = int(p.get("keep_groups", self.groups))
         self.correction_tensor = bool(p.get("correction", True))
+        self.routing = str(p.get("router", "scores"))         # "scores": a router product; "table": by token id
+        if self.routing not in ("scores", "table"):
+            raise ValueError(f"router {self.routing!r} is neither 'scores' nor 'table'")
+        self.vocab = int(p.get("vocab_size", 0))
+        if self.routing == "table" and (self.identity or self.vocab < 1):
+            raise ValueError("a routing table needs the vocabulary's size and takes no identity experts")
         self.E = self.experts + self.identity
         if self.experts < 1 or self.identity < 0:
             raise ValueError(f"{self.experts} experts and {self.identity} identity experts")
@@ -58,14 +67,17 @@ class RoutedFeedForward(Part):
             raise ValueError(f"{self.E} router outputs in {self.groups} groups of which {self.keep} stay")
         if not 1 <= self.top <= self.keep * (self.E // self.groups):
             raise ValueError(f"{self.top} choices among {self.keep * (self.E // self.groups)} open experts")
-        self.router = self.correction = None
+        self.router = self.correction = self.table = None
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
         n = self.name
-        out = {n + "router": ParamSpec((self.E, self.hidden), role="gain", init="normal")}
-        if self.correction_tensor:
+        if self.routing == "table":
+            out = {n + "table": ParamSpec((self.vocab, self.top), role="int", init="distinct", bounds=(0, self.experts))}
+        else:
+            out = {n + "router": ParamSpec((self.E, self.hidden), role="gain", init="normal")}
+        if self.correction_tensor and self.routing == "scores":
             out[n + "correction"] = ParamSpec((self.E,), role="gain", init="normal")
         for e in range(self.experts):
             out[f"{n}e{e}.gate"] = ParamSpec((self.inter, self.hidden))
@@ -75,8 +87,14 @@ class RoutedFeedForward(Part):
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
         n, F, d = self.name, self.inter, self.hidden
-        self.router = tensors[n + "router"]                  # float32: the router's product is never rounded
-        self.correction = tensors[n + "correction"] if self.correction_tensor else None
+        if self.routing == "table":
+            self.table = tensors[n + "table"]
+            lo, hi = int(self.table.min()), int(self.table.max())
+            if lo < 0 or hi >= self.experts:
+                raise ValueError(f"{n}table names experts {lo}..{hi}; there are {self.experts}")
+        else:
+            self.router = tensors[n + "router"]              # float32: the router's product is never rounded
+            self.correction = tensors[n + "correction"] if self.correction_tensor else None
         rows = [torch.stack([tensors[f"{n}e{e}.gate"], tensors[f"{n}e{e}.up"]], dim=1).reshape(2 * F, d)
                 for e in range(self.experts)]
         self.gate_up = Linear(torch.cat(rows, dim=0))
@@ -89,6 +107,10 @@ class RoutedFeedForward(Part):
         """float32 weights [N, E] (zero where an output was not chosen), ids int32 and weights float32 [N, top]."""
         N = x.shape[0]
         take = ctx.buffers.take
+        if self.routing == "table":
+            weights = take("moe_weights", N, (self.E,), torch.float32)
+            ops.moe_table(weights, ctx.token_ids, self.table, ctx.token_feedback)
+            return weights, None, None
         logits = take("moe_logits", N, (self.E,), torch.float32)
         ops.moe_logits(logits, x, self.router)
         weights = take("moe_weights", N, (self.E,), torch.float32)

@@ -111,7 +111,8 @@ class GatedSinkAttention(Part):
             proj, q, k_pool if self.own_kv else None, v_pool if self.own_kv else None, self.q_gain, self.k_gain,
             inv_freq, rotary_dim, ctx.positions, ctx.token_rows, table,
             self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, self.H, self.G, self.dk,
-            value_dim=self.dv, row_width=proj.shape[1], neighbours=self.position.neighbours)
+            value_dim=self.dv, row_width=proj.shape[1], neighbours=self.position.neighbours,
+            magnitude=getattr(self.position, "magnitude", 1.0))
         attn = ctx.buffers.take("sa_attn", N, (self.H * self.dv,), ctx.dtype)
         gate = proj[:, self.Cq + self.Ckv:] if self.gate is not None else None
         per_dim = self.gate == "dim"

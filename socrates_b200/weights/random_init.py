@@ -43,9 +43,21 @@ def random_tensors(expected: Mapping[str, ParamSpec], seed: int,
         elif spec.init == "uniform":
             lo, hi = spec.bounds
             out[name] = (lo + (hi - lo) * torch.rand(spec.draw_shape, generator=g)).to(torch.float32)
+        elif spec.init == "distinct":
+            out[name] = _distinct_rows(spec, g)
         else:
             raise ValueError(f"{name}: unknown init {spec.init!r}")
     return out
+
+
+def _distinct_rows(spec: ParamSpec, g: torch.Generator) -> torch.Tensor:
+    """An integer table whose rows hold different values from `bounds` = (lo, hi), hi exclusive."""
+    lo, hi = int(spec.bounds[0]), int(spec.bounds[1])
+    rows, k = spec.draw_shape
+    if k > hi - lo:
+        raise ValueError(f"{k} different values out of {hi - lo}")
+    order = torch.rand((rows, hi - lo), generator=g).argsort(dim=1)[:, :k]
+    return (order + lo).to(torch.int32)
 
 
 def write_model_folder(config, seed: int, out_dir, matrix_dtype: torch.dtype = torch.bfloat16) -> Path:
@@ -71,7 +83,9 @@ def random_tensors_on_device(expected: Mapping[str, ParamSpec], seed: int, dtype
     out: Dict[str, torch.Tensor] = {}
     for i, (name, spec) in enumerate(expected.items()):
         g.manual_seed(seed * 1000003 + i)
-        if spec.init == "gain":
+        if spec.init == "distinct":
+            out[name] = _distinct_rows(spec, _generator(seed, name)).to(device)
+        elif spec.init == "gain":
             out[name] = 1.0 + 0.1 * torch.randn(spec.draw_shape, generator=g, device=device, dtype=torch.float32)
         elif spec.init == "around_zero":
             out[name] = 0.1 * torch.randn(spec.draw_shape, generator=g, device=device, dtype=torch.float32)
