@@ -80,28 +80,33 @@ def diff_lambda(w: Mapping[str, torch.Tensor], pre: str, diff: float) -> float:
     return float(torch.exp((d("lq1") * d("lk1")).sum()) - torch.exp((d("lq2") * d("lk2")).sum()) + diff)
 
 
+def differential_heads(q, k, v, mask, scale: float, lam: float, diff: float, eps: float) -> torch.Tensor:
+    """q [T, H, 2, dim], k [T, G, 2, dim], v [T, G, vdim], mask [T, T] -> [T, H, vdim]: per head the difference of
+    two softmax maps over the same values, normed over the head's values, times (1 - diff)."""
+    H, G = q.shape[1], k.shape[1]
+    heads = []
+    for hd in range(H):
+        g = hd // (H // G)
+        a1 = softmax_map(q[:, hd, 0], k[:, g, 0], scale, mask) @ v[:, g]
+        a2 = softmax_map(q[:, hd, 1], k[:, g, 1], scale, mask) @ v[:, g]
+        heads.append(rms_norm(a1 - lam * a2, None, eps) * (1.0 - diff))
+    return torch.stack(heads, dim=1)
+
+
 def attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], pre: str, m: Mapping, eps: float) -> torch.Tensor:
     T = h.shape[0]
     H, G, dim, vdim = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     lin = lambda n: h @ w[pre + n].to(F64).T + w[pre + n + ".b"].to(F64)
-    q = lin("q").view(T, H, 2, dim)
-    k = lin("k").view(T, G, 2, dim)
-    v = lin("v").view(T, G, vdim)
     pos = torch.arange(T)
     rot = m.get("rot")
-    q = rotate(q.reshape(T, H * 2, dim), pos, rot).view(T, H, 2, dim)
-    k = rotate(k.reshape(T, G * 2, dim), pos, rot).view(T, G, 2, dim)
+    q = rotate(lin("q").view(T, H * 2, dim), pos, rot).view(T, H, 2, dim)
+    k = rotate(lin("k").view(T, G * 2, dim), pos, rot).view(T, G, 2, dim)
+    v = lin("v").view(T, G, vdim)
     mask_cfg = m.get("mask") or {}
     mask = visible(T, mask_cfg.get("size"), int(mask_cfg.get("keep_first", 0)))
     diff = float(m["diff"])
-    lam = diff_lambda(w, pre, diff)
-    heads = []
-    for hd in range(H):
-        g = hd // (H // G)
-        a1 = softmax_map(q[:, hd, 0], k[:, g, 0], float(m["scale"]), mask) @ v[:, g]
-        a2 = softmax_map(q[:, hd, 1], k[:, g, 1], float(m["scale"]), mask) @ v[:, g]
-        heads.append(rms_norm(a1 - lam * a2, None, eps) * (1.0 - diff))
-    return torch.cat(heads, dim=-1) @ w[pre + "o"].to(F64).T
+    o = differential_heads(q, k, v, mask, float(m["scale"]), diff_lambda(w, pre, diff), diff, eps)
+    return o.reshape(T, H * vdim) @ w[pre + "o"].to(F64).T
 
 
 def silu(z: torch.Tensor) -> torch.Tensor:
