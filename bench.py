@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 4b|8b|32b]
     python bench.py --compare bofusun [--sizes 1k,2k,4k]     (another design beside Qwen3 at equal size)
     python bench.py --compare loletar [--sizes 1k,2k,4k]
+    python bench.py --compare samerax [--sizes 1k,2k,4k]
 
 Default run: the layer sizes of the Qwen3-4B shape (36 layers, hidden 2560, 32 query
 heads over 8 KV heads, head_dim 128, intermediate 9728, vocabulary 151936, tied head),
@@ -430,6 +431,26 @@ def _loletar(width, heads):
             "embedding": {"scale": 1.0}, "layers": four + second}
 
 
+def _samerax(width, heads):
+    """A Samerax configuration at real layer widths, eight layer runs over four layers' weights: differential
+    attention with two maps of 64 dims a head (key rows of 128) and value heads of 128, a quarter as many KV heads,
+    all map dims rotating with stretched frequencies, a window of 4,096 keys that keeps the first 64 (every key of
+    the benchmark's contexts is visible, as in the Qwen3 model beside it); dense gated feed-forwards of four times the
+    width alternate with eight experts of twice the width chosen two a token by a table (the products a token
+    needs equal the dense feed-forward's)."""
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.6,
+           "rot": {"dims": 64, "base": 1e6, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+           "mask": {"size": 4096, "keep_first": 64}}
+    moe = {"kind": "moe", "expert": {"ff": 2 * width}, "router": {"experts": 8, "top": 2}}
+    four = [{"type": "attention", "mixer": dict(att), "mlp": {"kind": "dense", "ff": 4 * width}},
+            {"type": "attention", "mixer": dict(att), "mlp": moe},
+            {"type": "attention", "mixer": dict(att), "mlp": {"kind": "dense", "ff": 4 * width}},
+            {"type": "attention", "mixer": dict(att), "mlp": moe}]
+    again = [dict(l, weights_of=i) for i, l in enumerate(four)]
+    return {"architecture": "Samerax", "vocab": 32000, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "logit_softcap": 30.0, "layers": four + again}
+
+
 def _qwen3_like(width, runs, heads):
     """The Qwen3 decoder at the same width, number of layer runs, head size and feed-forward width."""
     return {"architectures": ["Qwen3ForCausalLM"], "vocab_size": 32000, "hidden_size": width,
@@ -439,7 +460,7 @@ def _qwen3_like(width, runs, heads):
 
 
 def run_compare(args):
-    """`--compare bofusun|loletar`: prefill and decode throughput of another design at real layer widths
+    """`--compare bofusun|loletar|samerax`: prefill and decode throughput of another design at real layer widths
     (random weights) beside the Qwen3 decoder at equal width, layer runs and head size.  One JSON line."""
     import torch
 
@@ -461,7 +482,8 @@ def run_compare(args):
     for size in wanted:
         width, heads = sizes[size]
         design = args.compare
-        bof = _bofusun(width, 5, heads, 1024) if design == "bofusun" else _loletar(width, heads)
+        bof = {"bofusun": lambda: _bofusun(width, 5, heads, 1024), "loletar": lambda: _loletar(width, heads),
+               "samerax": lambda: _samerax(width, heads)}[design]()
         runs = len(config_from_dict(bof).plan().order)
         only = [x for x in (args.only.split(",") if args.only else [design, "qwen3"])]
         for label, cfg_dict in ((design, bof), ("qwen3", _qwen3_like(width, runs, heads))):
@@ -585,7 +607,7 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
-    ap.add_argument("--compare", default=None, choices=("bofusun", "loletar"),
+    ap.add_argument("--compare", default=None, choices=("bofusun", "loletar", "samerax"),
                     help="the Bofusun or the Loletar design at real layer widths beside Qwen3 at equal size "
                          "(prefill and decode); the default workload is not run")
     ap.add_argument("--only", default=None, help="with --compare: run only these of the pair, e.g. 'loletar' or 'qwen3'")

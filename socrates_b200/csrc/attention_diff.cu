@@ -29,7 +29,8 @@ namespace {
 
 constexpr int THREADS = 128;
 constexpr int KEYS = 128;      // keys per chunk: one per thread
-constexpr int SUBS = 4;        // (head, map) rows per pass of the per-token kernel: two heads
+constexpr int SUBS = 8;        // (head, map) rows per pass of the per-token kernel: four heads, so that a group of
+                               // four query heads reads its keys and values once
 constexpr int DIMMAX = 128;    // dims of one map
 constexpr int ROWS = 32;       // (query, head, map) rows of a tile
 
@@ -216,24 +217,41 @@ __global__ void __launch_bounds__(THREADS) diff_merge_kernel(T* __restrict__ out
     __shared__ float red[33];
     const int h = blockIdx.x, n = blockIdx.y, tid = threadIdx.x;
     float a[2][2];                           // [map][dims tid, tid + THREADS]
+    // Loads go out eight at a time and none depends on another's value, so a merge costs a few round trips to
+    // L2 however many shares there are.
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
         const size_t base = (((size_t)n * H + h) * 2 + m) * NP;
         const float2* ml = reinterpret_cast<const float2*>(part_ml) + base;
         float M = -INFINITY;
-        for (int p = 0; p < NP; ++p) {
-            const float2 v = ml[p];
-            if (v.y > 0.f) M = fmaxf(M, v.x);
+        for (int p0 = 0; p0 < NP; p0 += 8) {
+            float2 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = p0 + j < NP ? ml[p0 + j] : make_float2(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (v[j].y > 0.f) M = fmaxf(M, v[j].x);
         }
         float L = 0.f, o0 = 0.f, o1 = 0.f;
-        for (int p = 0; p < NP; ++p) {
-            const float2 v = ml[p];
-            if (!(v.y > 0.f)) continue;
-            const float wgt = expf(v.x - M);
-            L += wgt * v.y;
-            const float* po = part_o + (base + p) * Dv;
-            if (tid < Dv) o0 += wgt * po[tid];
-            if (tid + THREADS < Dv) o1 += wgt * po[tid + THREADS];
+        for (int p0 = 0; p0 < NP; p0 += 8) {
+            float2 v[8];
+            float x0[8], x1[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = p0 + j < NP ? ml[p0 + j] : make_float2(0.f, 0.f);   // in L1 by now
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float* po = part_o + (base + p0 + j) * Dv;
+                x0[j] = (v[j].y > 0.f && tid < Dv) ? po[tid] : 0.f;                      // an empty share is never read
+                x1[j] = (v[j].y > 0.f && tid + THREADS < Dv) ? po[tid + THREADS] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (v[j].y > 0.f) {
+                    const float wgt = expf(v[j].x - M);
+                    L += wgt * v[j].y;
+                    o0 += wgt * x0[j];
+                    o1 += wgt * x1[j];
+                }
         }
         a[m][0] = o0 / L;
         a[m][1] = o1 / L;
@@ -411,6 +429,34 @@ __global__ void __launch_bounds__(THREADS, 4) diff_attention_tile_kernel(DiffTil
     }
 }
 
+// Two maps' outputs of a head, [a1 | a2] in float32 (the rows a tensor-core kernel left), to the head's output:
+// the difference, its RMS over the value dims, the scale.  A warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(THREADS) diff_combine_kernel(T* __restrict__ out, const float* __restrict__ maps, int rows,
+                                                              int Dv, float lambda, float eps, float out_scale) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    const int r = blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    const float* a1 = maps + (size_t)r * 2 * Dv;
+    const float* a2 = a1 + Dv;
+    float o[8];                                  // Dv <= 256
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int d = lane + 32 * j;
+        o[j] = d < Dv ? a1[d] - lambda * a2[d] : 0.f;
+        ss += o[j] * o[j];
+    }
+    ss = warp_sum(ss);
+    const float rr = out_scale / sqrtf(ss / (float)Dv + eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int d = lane + 32 * j;
+        if (d < Dv) out[(size_t)r * Dv + d] = from_float<T>(o[j] * rr);
+    }
+}
+
 int fill(DiffArgs& a, void* out, const void* q, const void* k_pool, const void* v_pool, const int* block_table,
          int table_width, const int* token_rows, const int* positions, int N, int H, int Hkv, int dim, int Dv,
          int page_size, int window, int keep_first, float scale, float lambda, float eps, float out_scale) {
@@ -492,5 +538,21 @@ extern "C" int sb_attention_diff_tile(void* out, const void* q, const void* k_po
         sb::launch(diff_attention_tile_kernel<float>, grid, dim3(THREADS), smem, stream, ta);
     else
         sb::launch(diff_attention_tile_kernel<__nv_bfloat16>, grid, dim3(THREADS), smem, stream, ta);
+    SB_LAUNCH_CHECK();
+}
+
+// maps float32 [N, H, 2, Dv] -> out [N, H, Dv] in the model dtype.
+extern "C" int sb_diff_combine(void* out, const float* maps, int N, int H, int Dv, float lambda, float eps,
+                               float out_scale, int dtype, cudaStream_t stream) {
+    SB_REQUIRE(N >= 0 && H > 0 && Dv >= 1 && Dv <= 256, "diff_combine: bad sizes N=%d H=%d Dv=%d", N, H, Dv);
+    SB_REQUIRE(dtype == SB_F32 || dtype == SB_BF16, "diff_combine: unknown dtype %d", dtype);
+    if (N == 0) return 0;
+    const int rows = N * H, blocks = (rows + THREADS / 32 - 1) / (THREADS / 32);
+    if (dtype == SB_F32)
+        sb::launch(diff_combine_kernel<float>, dim3(blocks), dim3(THREADS), 0, stream, (float*)out, maps, rows, Dv, lambda,
+                   eps, out_scale);
+    else
+        sb::launch(diff_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(THREADS), 0, stream, (__nv_bfloat16*)out, maps,
+                   rows, Dv, lambda, eps, out_scale);
     SB_LAUNCH_CHECK();
 }

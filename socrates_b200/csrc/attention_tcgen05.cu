@@ -192,7 +192,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                             const int* __restrict__ seq_starts, const int* __restrict__ seq_rows,
                             const int* __restrict__ seq_first_pos, int R, int Hq, int Hkv, int BS, int window,
                             float scale_log2, int* __restrict__ status, const bf16* __restrict__ gate,
-                            long long gate_stride, int gate_per_dim, int has_sink, float sink_raw) {
+                            long long gate_stride, int gate_per_dim, int has_sink, float sink_raw, int keep_first,
+                            float* __restrict__ out_f32) {
     constexpr int PANELS = D / 64;                         // 64-dim panels of 128-byte rows
     constexpr int PANEL_Q = ROWS * 128;                    // bytes of one Q panel
     constexpr int PANEL_KV = KTILE * 128;                  // bytes of one K or V panel
@@ -255,14 +256,18 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
         tile -= tiles;
     }
     const bool active = r < R;
-    int first_pos = 0, lo = 0, hi = 0, tile_begin = 0, n_tiles = 0, table_base = 0, table_count = 0;
+    int first_pos = 0, lo = 0, hi = 0, tile_begin = 0, n_tiles = 0, table_base = 0, table_count = 0, keep_tiles = 0;
+    // a window may keep the first `kf` keys of the row beside it: the key tiles that hold them run first
+    // (`keep_tiles` of them, only those that lie wholly before the window's first tile), then the window's
+    const int kf = window > 0 ? keep_first : 0;
     if (active) {
         first_pos = seq_first_pos[r] + tile * TQ;
         hi = first_pos + n_tok;
         lo = (window > 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
         tile_begin = lo / KTILE;
-        n_tiles = (hi + KTILE - 1) / KTILE - tile_begin;
-        table_base = lo >> bs_log2;
+        keep_tiles = min((kf + KTILE - 1) / KTILE, tile_begin);
+        n_tiles = (hi + KTILE - 1) / KTILE - tile_begin + keep_tiles;
+        table_base = kf > 0 ? 0 : lo >> bs_log2;
         table_count = ((hi - 1) >> bs_log2) - table_base + 1;
         const int* table = block_table + (size_t)seq_rows[r] * table_width;
         for (int i = tid; i < table_count; i += THREADS) stab[i] = table[table_base + i];
@@ -304,7 +309,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                 const int pg = lane / PANELS, p = lane - pg * PANELS;
                 int y = 0;
                 if (lane < n_ops) {
-                    const int logical = (((tile_begin + t) * KTILE) >> bs_log2) + pg - table_base;
+                    const int kt = t < keep_tiles ? t : tile_begin + t - keep_tiles;
+                    const int logical = ((kt * KTILE) >> bs_log2) + pg - table_base;
                     const int phys = (logical >= 0 && logical < table_count) ? stab[logical] : 0;
                     y = (phys * Hkv + kh) * BS;
                 }
@@ -399,7 +405,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
         bool ok = true;
         for (int i = 0; i < n_tiles; ++i) {
             const int b = i & 1;
-            const int tile_start = (tile_begin + i) * KTILE;
+            const int tile_start = (i < keep_tiles ? i : tile_begin + i - keep_tiles) * KTILE;
             bool got = mbar_wait(smem_u32(&s_full[b]), (i >> 1) & 1);
             if (*((volatile int*)&abort_flag)) got = false;
             got = __all_sync(0xffffffffu, got);
@@ -420,12 +426,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
             }
             // position masks only where some row of the block cannot see some key of the tile;
             // rows past the tile (qpos = -1) are masked by the same test
-            const bool masked = tile_start + KTILE - 1 > first_pos || tile_start < last_qlo || n_tok < TQ;
+            const bool masked = i < keep_tiles ? (tile_start + KTILE > kf || n_tok < TQ)
+                                               : (tile_start + KTILE - 1 > first_pos || tile_start < last_qlo || n_tok < TQ);
             if (masked) {
 #pragma unroll
                 for (int j = 0; j < 64; ++j) {
                     const int kpos = tile_start + j;
-                    s[j] = (kpos <= qpos && kpos >= qlo) ? s[j] : -INFINITY;
+                    s[j] = (kpos <= qpos && (kpos >= qlo || kpos < kf)) ? s[j] : -INFINITY;
                 }
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -496,7 +503,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                 if (!landed) { ok = false; if ((tid & 31) == 0) { atomicExch(status, 14); atomicExch(&abort_flag, 1); } break; }
                 if (tid < KTILE) {
                     const int kpos = tile_start + tid;
-                    if (kpos < lo || kpos >= hi) {
+                    if ((kpos < lo && kpos >= kf) || kpos >= hi) {
 #pragma unroll
                         for (int p = 0; p < PANELS; ++p) {
                             uint4* row = reinterpret_cast<uint4*>(gen_base + q_bytes<D>() + 2 * kv_bytes<D>() +
@@ -531,6 +538,22 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
             } else {
                 tc_fence_after();
                 const float inv = 1.0f / l_run;
+                if (out_f32 != nullptr) {
+                    // the rows as they are, in float32: whoever asked for them combines heads before rounding
+                    float4* dstf = reinterpret_cast<float4*>(out_f32 + ((size_t)(t0 + (tok < n_tok ? tok : 0)) * Hq + kh * G + g) * D);
+#pragma unroll
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t ov[32];
+                        tmem_ld32(lane_base + COL_O + c, ov);
+                        tmem_ld_wait();
+                        if (tok < n_tok) {
+                            const float* f = reinterpret_cast<const float*>(ov);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                dstf[c / 4 + j] = make_float4(f[4 * j] * inv, f[4 * j + 1] * inv, f[4 * j + 2] * inv, f[4 * j + 3] * inv);
+                        }
+                    }
+                } else {
                 uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(t0 + (tok < n_tok ? tok : 0)) * Hq + kh * G + g) * D);
                 // an output gate: sigmoid of one value per head, or per head and dim
                 const bf16* grow_ptr = gate ? gate + (size_t)(t0 + (tok < n_tok ? tok : 0)) * gate_stride +
@@ -569,6 +592,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                         }
                     }
                 }
+                }
             }
         }
     }
@@ -590,7 +614,7 @@ template <int D>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, void* out, const void* q, const int* block_table,
            int table_width, const int* seq_starts, const int* seq_rows, const int* seq_first_pos, int R, int N,
            int Hq, int Hkv, int BS, int window, float scale, int* status, const void* gate, long long gate_stride,
-           int gate_per_dim, int has_sink, float sink, cudaStream_t stream) {
+           int gate_per_dim, int has_sink, float sink, int keep_first, float* out_f32, cudaStream_t stream) {
     auto kernel = attn_prefill_tcgen05_kernel<D>;
     static sb::OncePerDevice once_per_device;
     bool& configured = once_per_device.flag();
@@ -605,7 +629,7 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, void* out, const void* 
     sb::launch(kernel, grid, dim3(THREADS), smem_bytes<D>() + table_width * 4, stream, mk, mv, (bf16*)out,
                (const bf16*)q, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, Hq, Hkv, BS, window,
                scale * LOG2E, status, (const bf16*)gate, gate_stride, gate_per_dim, has_sink,
-               has_sink ? sink / scale : 0.f);
+               has_sink ? sink / scale : 0.f, keep_first, out_f32);
     return 0;
 }
 
@@ -622,14 +646,17 @@ extern "C" int sb_attention_tcgen05_supports(int Hq, int Hkv, int D, int page_si
 // Arguments as sb_attention_prefill_mma, plus `num_pages` (pages of the pools, the null
 // page included) and the status word of the bounded waits.  Optional: a sigmoid output gate
 // (`gate` [N, gate_stride] bfloat16, one column per head, or per head and dim) and a sink (a score
-// whose exponential joins the denominator without a value).
+// whose exponential joins the denominator without a value); `keep_first`: a window also sees the first
+// so many keys of its row; `out_f32` (float32 [N, Hq*D], or null): the rows are written there unrounded
+// and ungated instead of to `out`.
 extern "C" int sb_attention_prefill_tcgen05(void* out, const void* q, const void* k_pool, const void* v_pool,
                                             int num_pages, const int* block_table, int table_width,
                                             const int* seq_starts, const int* seq_rows,
                                             const int* seq_first_pos, int R, int N, int Hq, int Hkv, int D,
                                             int page_size, int window, float scale, int* status,
                                             const void* gate, long long gate_stride, int gate_per_dim, int has_sink,
-                                            float sink, cudaStream_t stream) {
+                                            float sink, int keep_first, float* out_f32, cudaStream_t stream) {
+    SB_REQUIRE(keep_first >= 0, "attention_tcgen05: %d kept keys", keep_first);
     SB_REQUIRE(!has_sink || scale > 0.f, "attention_tcgen05: a sink needs a positive scale");
     if (gate != nullptr && gate_per_dim && (reinterpret_cast<uintptr_t>(gate) & 15) == 0 && gate_stride % 8 == 0)
         gate_per_dim = 2;                                  // 16-byte loads of the gate
@@ -648,10 +675,10 @@ extern "C" int sb_attention_prefill_tcgen05(void* out, const void* q, const void
     int rc;
     if (D == 64)
         rc = launch<64>(mk, mv, out, q, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, N, Hq, Hkv,
-                        page_size, window, scale, status, gate, gate_stride, gate_per_dim, has_sink, sink, stream);
+                        page_size, window, scale, status, gate, gate_stride, gate_per_dim, has_sink, sink, keep_first, out_f32, stream);
     else
         rc = launch<128>(mk, mv, out, q, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, N, Hq,
-                         Hkv, page_size, window, scale, status, gate, gate_stride, gate_per_dim, has_sink, sink, stream);
+                         Hkv, page_size, window, scale, status, gate, gate_stride, gate_per_dim, has_sink, sink, keep_first, out_f32, stream);
     if (rc != 0) return rc;
     SB_LAUNCH_CHECK();
 }

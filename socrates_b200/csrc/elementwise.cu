@@ -256,7 +256,8 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
 // `bias` (float32, one entry per input column, or null) is added to the input first.  A query or
 // key head may hold several maps of `sub` dims each (sub divides D): every map rotates its own
 // first R dims.  `magnitude` multiplies every cosine and sine (an encoding that also scales the
-// rotated dims); dims that do not rotate are not scaled.
+// rotated dims); dims that do not rotate are not scaled.  With `spread` the queries are written one
+// row per (head, map), [N, Hq * maps, D]: the map's dims where they are and zeros elsewhere.
 template <typename T>
 __global__ void qk_norm_rope_kvwrite_kernel(
     const T* __restrict__ qkv, const float* __restrict__ parts, int S, size_t part_stride,
@@ -265,7 +266,7 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     const float* __restrict__ inv_freq, int R, const int* __restrict__ positions,
     const int* __restrict__ token_rows, const int* __restrict__ block_table, int table_width,
     int BS, float eps, int Hq, int Hkv, int D, int write_kv, int Dv, int row_width, int neighbours,
-    const float* __restrict__ bias, int sub, float magnitude) {
+    const float* __restrict__ bias, int sub, float magnitude, int spread) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     __shared__ float buf[4][256];
@@ -307,8 +308,9 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     __syncwarp();
 
     T* dst;
+    const int maps = D / sub;
     if (is_q) {
-        dst = q_out + ((size_t)n * Hq + head) * D;
+        dst = q_out + ((size_t)n * Hq + head) * D * (spread ? maps : 1);
     } else {
         const int kh = is_k ? head - Hq : head - Hq - Hkv;
         const int row = token_rows[n];
@@ -329,7 +331,12 @@ __global__ void qk_norm_rope_kvwrite_kernel(
             const float c = cosf(ang) * magnitude, s = sinf(ang) * magnitude;
             o = first ? y[i] * c - y[mate] * s : y[i] * c + y[mate] * s;
         }
-        dst[i] = from_float<T>(o);
+        if (is_q && spread) {
+            // a row per map: the map's dims in their place, zeros where the other maps' dims are
+            for (int m = 0; m < maps; ++m) dst[(size_t)m * D + i] = from_float<T>(m == i / sub ? o : 0.f);
+        } else {
+            dst[i] = from_float<T>(o);
+        }
     }
 }
 
@@ -556,11 +563,11 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
                       int rotary_dim, const int* positions, const int* token_rows, const int* block_table,
                       int table_width, int page_size, float eps, int Hq, int Hkv, int D, int N, int write_kv,
                       int Dv, int row_width, int neighbours, const float* bias, int sub, float magnitude,
-                      cudaStream_t stream) {
+                      int spread, cudaStream_t stream) {
     const int n_heads = Hq + 2 * Hkv;
     const bool fast = (rotary_dim == D || rotary_dim == 0) && (D == 64 || D == 128 || D == 256) && Dv == D &&
                       row_width == n_heads * D && !(neighbours && rotary_dim > 0) && bias == nullptr && sub == D &&
-                      magnitude == 1.0f;
+                      magnitude == 1.0f && !spread;
     // Heads per block: 4 (a head per warp) while that still fills the GPU, more for long batches.
     int hpb = 4;
     if (fast) {
@@ -585,7 +592,7 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
     else if (fast) { SB_QK_FAST(8) }
 #undef SB_QK_FAST
     else sb::launch(qk_norm_rope_kvwrite_kernel<T>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, D, write_kv, Dv,
-                    row_width, neighbours, bias, sub, magnitude);
+                    row_width, neighbours, bias, sub, magnitude, spread);
 #undef SB_QK_ARGS
 }
 
@@ -598,7 +605,7 @@ extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, const float* parts, int 
                                        const int* token_rows, const int* block_table, int table_width,
                                        int page_size, float eps, int Hq, int Hkv, int D, int N,
                                        int write_kv, int dtype, int Dv, int row_width, int neighbours,
-                                       const float* bias, int sub, float magnitude, cudaStream_t stream) {
+                                       const float* bias, int sub, float magnitude, int spread, cudaStream_t stream) {
     if (sub <= 0) sub = D;
     SB_REQUIRE(D % sub == 0 && rotary_dim <= sub, "qk_norm_rope: heads of %d dims do not hold maps of %d with %d rotating",
                D, sub, rotary_dim);
@@ -617,11 +624,11 @@ extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, const float* parts, int 
     if (dtype == SB_F32)
         qk_launch<float>(qkv, parts, S, (size_t)part_stride, q_out, k_pool, v_pool, q_gain, k_gain, inv_freq,
                          rotary_dim, positions, token_rows, block_table, table_width, page_size, eps, Hq, Hkv, D, N,
-                         write_kv, Dv, row_width, neighbours, bias, sub, magnitude, stream);
+                         write_kv, Dv, row_width, neighbours, bias, sub, magnitude, spread, stream);
     else if (dtype == SB_BF16)
         qk_launch<__nv_bfloat16>(qkv, parts, S, (size_t)part_stride, q_out, k_pool, v_pool, q_gain, k_gain,
                                  inv_freq, rotary_dim, positions, token_rows, block_table, table_width, page_size,
-                                 eps, Hq, Hkv, D, N, write_kv, Dv, row_width, neighbours, bias, sub, magnitude, stream);
+                                 eps, Hq, Hkv, D, N, write_kv, Dv, row_width, neighbours, bias, sub, magnitude, spread, stream);
     else
         SB_REQUIRE(false, "qk_norm_rope: unknown dtype %d", dtype);
     SB_LAUNCH_CHECK();

@@ -30,7 +30,7 @@ _SIGNATURES = {
     "sb_set_dependent_launch": [I],
     "sb_embed": [P, P, P, I, I, I, I, P, F, P],
     "sb_add_rmsnorm": [P, P, I, LL, P, P, P, I, I, F, I, P],
-    "sb_qk_norm_rope_kvwrite": [P, P, I, LL, P, P, P, P, P, P, I, P, P, P, I, I, F, I, I, I, I, I, I, I, I, I, P, I, F, P],
+    "sb_qk_norm_rope_kvwrite": [P, P, I, LL, P, P, P, P, P, P, I, P, P, P, I, I, F, I, I, I, I, I, I, I, I, I, P, I, F, I, P],
     "sb_silu_mul": [P, P, I, I, I, I, P],
     "sb_sample": [P, P, P, P, P, I, I, P, P],
     "sb_sample_slices": [I],
@@ -47,7 +47,7 @@ _SIGNATURES = {
     "sb_attention_decode_stream_supports": [I, I, I, I],
     "sb_attention_decode_stream": [P, P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "sb_attention_tcgen05_supports": [I, I, I, I],
-    "sb_attention_prefill_tcgen05": [P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P, LL, I, I, F, P],
+    "sb_attention_prefill_tcgen05": [P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P, LL, I, I, F, I, P, P],
     "sb_fold_rmsnorm": [P, P, I, LL, P, P, F, P, P, P, P, P, I, I, F, I, P],
     "sb_normed_mean": [P, P, I, LL, P, P, I, LL, P, I, I, F, F, P],
     "sb_bias_act": [P, P, P, I, LL, P, I, I, I, I, P],
@@ -65,6 +65,7 @@ _SIGNATURES = {
     "sb_moe_passthrough": [P, P, P, I, I, I, I, I, P],
     "sb_attention_bias_tile": [P, P, P, P, P, I, P, P, P, I, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, I, I, F, P],
     "sb_softcap": [P, LL, F, P],
+    "sb_diff_combine": [P, P, I, I, I, F, F, F, I, P],
     "sb_moe_table": [P, P, P, P, I, I, I, I, P],
     "sb_attention_diff": [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, F, F, F, I, P, P, I, P],
     "sb_attention_diff_tile_supports": [I, I, I, I, I],

@@ -125,7 +125,7 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
                          eps: float, num_heads: int, num_kv_heads: int, head_dim: int,
                          value_dim: Optional[int] = None, row_width: Optional[int] = None,
                          neighbours: bool = False, bias: Optional[torch.Tensor] = None,
-                         map_dim: Optional[int] = None, magnitude: float = 1.0) -> None:
+                         map_dim: Optional[int] = None, magnitude: float = 1.0, spread_maps: bool = False) -> None:
     """Per-head norm, rotation and paged KV write for N tokens.
 
     qkv [N, (Hq+2Hkv)*D] in the model dtype, or float32 [S, N, (Hq+2Hkv)*D] partial sums
@@ -137,6 +137,8 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
     instead of dim j with dim j + rotary_dim/2.  `bias`: float32 [row_width], added to the input
     columns first.  `map_dim`: a query or key head holds head_dim / map_dim maps, each of which
     rotates its own first rotary_dim dims.  `magnitude` multiplies every cosine and sine.
+    `spread_maps`: q_out is [N, Hq * maps, head_dim], a row per (head, map) that holds the map's dims in
+    their place and zeros elsewhere, so that a dot product with a whole key row gives that map's score.
     """
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     Dv = D if value_dim is None else int(value_dim)
@@ -147,7 +149,8 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
         _want(qkv, "qkv partial sums", torch.float32, (qkv.shape[0], N, width))
     else:
         _want(qkv, "qkv", q_out.dtype, (N, width))
-    _want(q_out, "q_out", None, (N, Hq * D))
+    maps_out = (D // int(map_dim)) if (spread_maps and map_dim) else 1
+    _want(q_out, "q_out", None, (N, Hq * D * maps_out))
     _want(positions, "positions", torch.int32, (N,))
     _want(token_rows, "token_rows", torch.int32, (N,))
     _want(block_table, "block_table", torch.int32)
@@ -176,7 +179,7 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
         N * width, _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq),
         rotary_dim, _ptr(positions), _ptr(token_rows), _ptr(block_table), block_table.shape[1],
         page_size, float(eps), Hq, Hkv, D, N, int(write_kv), _code(q_out.dtype), Dv, width, int(neighbours),
-        _ptr(bias), sub, float(magnitude), _stream()), "qk_norm_rope_kvwrite")
+        _ptr(bias), sub, float(magnitude), int(bool(spread_maps)), _stream()), "qk_norm_rope_kvwrite")
 
 
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, interleaved: bool = False) -> None:
@@ -465,15 +468,23 @@ def attention_prefill_tcgen05(out: torch.Tensor, q: torch.Tensor, k_pool: torch.
                               block_table: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor,
                               seq_first_pos: torch.Tensor, num_heads: int, scale: float, status: torch.Tensor,
                               window: int = 0, gate: Optional[torch.Tensor] = None, gate_per_dim: bool = False,
-                              sink: Optional[float] = None) -> None:
+                              sink: Optional[float] = None, keep_first: int = 0,
+                              out_float: Optional[torch.Tensor] = None) -> None:
     """Paged causal attention of prompt portions on tcgen05 (scores and P.V in tensor
     memory, pages brought in by TMA).  Arguments as `attention_prefill_mma`, plus the int32
-    status word that receives a non-zero code if a bounded wait inside the kernel gave up."""
+    status word that receives a non-zero code if a bounded wait inside the kernel gave up.
+    `keep_first`: a window also sees the first so many keys of its row.  `out_float` (float32
+    [N, Hq*D]): the rows go there unrounded instead of to `out` (which may then be None)."""
     N = q.shape[0]
     pages, Hkv, BS, D = k_pool.shape
     R = seq_rows.numel()
     _want(q, "q", torch.bfloat16, (N, num_heads * D))
-    _want(out, "out", torch.bfloat16, (N, num_heads * D))
+    if out_float is not None:
+        _want(out_float, "out_float", torch.float32, (N, num_heads * D))
+        if gate is not None:
+            raise KernelError("the float32 rows are written ungated")
+    else:
+        _want(out, "out", torch.bfloat16, (N, num_heads * D))
     _want(k_pool, "k_pool", torch.bfloat16)
     _want(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
     _want(block_table, "block_table", torch.int32)
@@ -489,7 +500,7 @@ def attention_prefill_tcgen05(out: torch.Tensor, q: torch.Tensor, k_pool: torch.
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_table), block_table.shape[1],
         _ptr(seq_starts), _ptr(seq_rows), _ptr(seq_first_pos), R, N, num_heads, Hkv, D, BS, int(window),
         float(scale), _ptr(status), _ptr(gate), gate_stride, int(gate_per_dim), int(sink is not None),
-        float(sink or 0.0), _stream()), "attention_prefill_tcgen05")
+        float(sink or 0.0), int(keep_first), _ptr(out_float), _stream()), "attention_prefill_tcgen05")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -1037,3 +1048,15 @@ def attention_diff_tile(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor
                                           R, N, num_heads, Hkv, dim, Dv, BS, int(window), int(keep_first), float(scale),
                                           float(lam), float(eps), float(out_scale), _code(q.dtype), _stream()),
           "attention_diff_tile")
+
+
+def diff_combine(out: torch.Tensor, maps: torch.Tensor, num_heads: int, lam: float, eps: float, out_scale: float) -> None:
+    """maps float32 [N, H*2*Dv] holds per head the outputs of its two maps, [a1 | a2]:
+    out[n, h] = o / sqrt(mean(o^2) + eps) * out_scale with o = a1 - lam * a2; out [N, H*Dv] in the model dtype."""
+    N = maps.shape[0]
+    Dv = maps.shape[1] // (2 * num_heads)
+    _want(maps, "maps", torch.float32, (N, num_heads * 2 * Dv))
+    _want(out, "out", None, (N, num_heads * Dv))
+    lib = library()
+    check(lib, lib.sb_diff_combine(_ptr(out), _ptr(maps), N, num_heads, Dv, float(lam), float(eps), float(out_scale),
+                                   _code(out.dtype), _stream()), "diff_combine")

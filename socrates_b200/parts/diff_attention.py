@@ -96,18 +96,33 @@ class DifferentialAttention(Part):
     def forward(self, ctx, x: torch.Tensor, cache) -> Branch:
         N = x.shape[0]
         proj = self.proj(ctx, x, "da_proj", out="model_or_partial")
-        q = ctx.buffers.take("da_q", N, (self.Cq,), ctx.dtype)
         k_pool, v_pool = cache.pools()
         table = cache.block_table()
         inv_freq, rotary_dim = self.position.tables(x.device)
+        # Prompt portions in the bfloat16 engine, key rows and value heads of one size of 64 or 128: the tensor-core
+        # tile kernel.  Every (head, map) is a query row of its own that holds its map's dims and zeros where the
+        # other map's are, so the product with a whole key row is that map's score (adding zeros is exact); scores
+        # are float32 sums over the bfloat16 q and k that the cache holds anyway, softmax is float32, each weight
+        # enters the value product as two bfloat16 terms, and both maps' rows come back in float32 for the
+        # difference and the head norm.
+        tensor_cores = (not ctx.all_decode and N >= 4 * ctx.num_seqs and ctx.dtype == torch.bfloat16
+                        and ctx.status is not None and 2 * self.dim == self.dv
+                        and ops.attention_tcgen05_supports(2 * self.H, self.G, self.dv, k_pool.shape[2]))
+        q = ctx.buffers.take("da_q", N, (self.Cq * (2 if tensor_cores else 1),), ctx.dtype)
         ops.qk_norm_rope_kvwrite(
             proj, q, k_pool if cache.writes else None, v_pool if cache.writes else None, None, None,
             inv_freq, rotary_dim, ctx.positions, ctx.token_rows, table, 0.0, self.H, self.G, 2 * self.dim,
             value_dim=self.dv, row_width=self.Cq + self.Ck + self.Cv, bias=self.proj_bias, map_dim=self.dim,
-            magnitude=self.position.magnitude)
+            magnitude=self.position.magnitude, spread_maps=tensor_cores)
         attn = ctx.buffers.take("da_attn", N, (self.H * self.dv,), ctx.dtype)
         window, out_scale = self.window or 0, 1.0 - self.diff
-        if (not ctx.all_decode and N >= 4 * ctx.num_seqs
+        if tensor_cores:
+            maps = ctx.buffers.take("da_maps", N, (self.H * 2 * self.dv,), torch.float32)
+            ops.attention_prefill_tcgen05(None, q, k_pool, v_pool, table, ctx.seq_starts, ctx.seq_rows,
+                                          ctx.seq_first_pos, 2 * self.H, self.scale, ctx.status, window,
+                                          keep_first=self.keep_first, out_float=maps)
+            ops.diff_combine(attn, maps, self.H, self.lam, self.eps, out_scale)
+        elif (not ctx.all_decode and N >= 4 * ctx.num_seqs
                 and ops.attention_diff_tile_supports(self.H, self.G, self.dim, self.dv, ctx.dtype)):
             # prompt portions: a tile of a request's consecutive tokens per block shares the keys it reads
             ops.attention_diff_tile(attn, q, k_pool, v_pool, table, ctx.seq_starts, ctx.seq_rows, ctx.seq_first_pos,

@@ -2,7 +2,8 @@
 
 The configurations differ from one another in every size and option: head counts and groups of 1, 2
 and 3 query heads per key/value head, maps of 8 to 128 dims (multiples of the 16-byte vector and not),
-value heads smaller than, equal to and larger than a key row (one beyond 128 dims), full, partial
+value heads smaller than, equal to and larger than a key row (one beyond 128 dims; equal ones of 64 and 128 that the
+bfloat16 engine serves on the tensor cores), full, partial
 and no rotation, with and without stretched frequencies, windows shorter than a page, longer than a
 chunk of 128 keys and absent, kept first keys of 0, 1, a whole page and more than the window, dense,
 routed and no feed-forwards, top-1, top = every expert, layers that run an earlier layer's weights
@@ -46,7 +47,8 @@ def _layer(mixer, mlp, weights_of=None):
 _A0 = _att(6, 2, 8, 24, 0.4, 0.3, rot=6, base=100.0, scaling=(4.0, 32, 8.0, 1.0), size=37, keep=5)
 _A1 = _att(2, 1, 16, 8, 0.3, 0.7, size=20, keep=0)
 _C0 = _att(4, 2, 64, 32, 0.15, 0.45, rot=32, base=50000.0, scaling=(8.0, 64, 4.0, 0.5), size=130, keep=33)
-_D0 = _att(2, 1, 128, 128, 0.1, 0.25, rot=64, base=1000.0, size=300, keep=1)
+_D0 = _att(2, 1, 64, 128, 0.1, 0.25, rot=64, base=1000.0, size=100, keep=65)
+_D1 = _att(6, 3, 32, 64, 0.2, 0.4, rot=8, base=100.0, scaling=(2.0, 16, 4.0, 1.0), size=70, keep=9)
 
 TINY = {
     # three query heads a group, partial stretched rotation, a window with a few kept keys; layers run again
@@ -67,9 +69,10 @@ TINY = {
     "C": {"architecture": "Samerax", "vocab": 300, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.5},
           "logit_softcap": 8.0,
           "layers": [_layer(_C0, _moe(32, 4, 3)), _layer(_C0, _moe(32, 4, 3), 0), _layer(_C0, _dense(72))]},
-    # maps and values of 128 dims, one KV head, one kept key, a single layer
-    "D": {"architecture": "Samerax", "vocab": 80, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0},
-          "logit_softcap": 50.0, "layers": [_layer(_D0, _dense(64))]},
+    # key rows and value heads of one size, 128 and 64: in the bfloat16 engine prompt portions of these layers run on
+    # the tensor-core attention kernel; kept keys that fill a key tile of 64 and one more, and a few only
+    "D": {"architecture": "Samerax", "vocab": 80, "width": 96, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0},
+          "logit_softcap": 50.0, "layers": [_layer(_D0, _dense(64)), _layer(_D1, _moe(24, 3, 2)), _layer(_D0, _dense(64), 0)]},
 }
 
 

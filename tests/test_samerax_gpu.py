@@ -85,6 +85,14 @@ def test_bias_rotation_of_every_map_with_a_magnitude_and_cache_write(dtype, shap
                                  table, 0.0, H, G, 2 * dim, value_dim=Dv, row_width=width, bias=bias.to(DEV),
                                  map_dim=dim, magnitude=mag)
         assert torch.allclose(q.double().cpu().view(N, H, 2 * dim), want_q, atol=tol, rtol=tol)
+        # the same queries, a row per (head, map): the map's dims in their place, zeros elsewhere
+        wide = torch.full((N, H * 4 * dim), 7.0, device=DEV, dtype=dtype)
+        ops.qk_norm_rope_kvwrite(source, wide, None, None, None, None, freq.float().to(DEV), R, i32(pos), i32(rows),
+                                 table, 0.0, H, G, 2 * dim, value_dim=Dv, row_width=width, bias=bias.to(DEV),
+                                 map_dim=dim, magnitude=mag, spread_maps=True)
+        wide = wide.view(N, H, 2, 2, dim)
+        assert torch.equal(wide[:, :, 0, 0], q.view(N, H, 2, dim)[:, :, 0]) and torch.equal(wide[:, :, 1, 1], q.view(N, H, 2, dim)[:, :, 1])
+        assert not bool(wide[:, :, 0, 1].any()) and not bool(wide[:, :, 1, 0].any())
         pages = {2: [1, 3], 0: [5, 0]}
         for n in range(N):
             pg, off = pages[rows[n]][pos[n] // page], pos[n] % page
@@ -93,10 +101,12 @@ def test_bias_rotation_of_every_map_with_a_magnitude_and_cache_write(dtype, shap
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(6, 2, 8, 24), (2, 1, 16, 8), (3, 3, 12, 40), (2, 2, 24, 130), (4, 2, 64, 32)])
-@pytest.mark.parametrize("mask", [(0, 0), (7, 0), (7, 3), (130, 9), (16, 16), (5, 40)])
+@pytest.mark.parametrize("shape", [(6, 2, 8, 24), (2, 1, 16, 8), (3, 3, 12, 40), (2, 2, 24, 130), (4, 2, 64, 32),
+                                   (6, 3, 32, 64), (2, 1, 64, 128)])
+@pytest.mark.parametrize("mask", [(0, 0), (7, 0), (7, 3), (130, 9), (16, 16), (5, 40), (100, 65), (70, 130)])
 def test_differential_attention_kernels(dtype, shape, mask):
-    """The three forms (a block a token, key shares that are merged, tiles of a prompt portion) against the plain
+    """The forms of the kernel (a block a token, key shares that are merged, tiles of a prompt portion on the CUDA
+    cores and, in bfloat16 with key rows and value heads of one size, on the tensor cores) against the plain
     difference of two softmax maps, for two requests in scattered pages: a whole prompt, and a portion behind
     an earlier one."""
     from socrates_b200.kernels import ops
@@ -104,12 +114,12 @@ def test_differential_attention_kernels(dtype, shape, mask):
     window, keep = mask
     page, scale, lam, diff, eps = 16, 0.7, 0.8, 0.35, 1e-5
     g = torch.Generator().manual_seed(sum(shape) + window)
-    lens, new = [150, 41], [150, 6]                       # request 1: 35 tokens are in the cache already
-    pools_k, pools_v, qs, wants = [], [], [], []
-    order = torch.randperm(14, generator=g).tolist()      # pages 1..14 scattered over the two requests
-    tables = [[1 + o for o in order[:10]], [1 + o for o in order[10:13]] + [0] * 7]
-    k_pool = torch.zeros(15, G, page, 2 * dim, dtype=dtype)
-    v_pool = torch.zeros(15, G, page, Dv, dtype=dtype)
+    lens, new = [330, 41], [330, 6]                       # request 1: 35 tokens are in the cache already
+    qs, wants = [], []
+    order = torch.randperm(25, generator=g).tolist()      # pages 1..25 scattered over the two requests
+    tables = [[1 + o for o in order[:21]], [1 + o for o in order[21:24]] + [0] * 18]
+    k_pool = torch.zeros(26, G, page, 2 * dim, dtype=dtype)
+    v_pool = torch.zeros(26, G, page, Dv, dtype=dtype)
     for r, n in enumerate(lens):
         q = torch.randn(n, H, 2, dim, generator=g).to(dtype)
         k = torch.randn(n, G, 2, dim, generator=g).to(dtype)
@@ -142,6 +152,20 @@ def test_differential_attention_kernels(dtype, shape, mask):
         assert part_err(out.double().cpu(), want) < tol
     else:
         assert Dv > 128 or dim % (8 if dtype == torch.bfloat16 else 4)
+    if dtype == torch.bfloat16 and 2 * dim == Dv and ops.attention_tcgen05_supports(2 * H, G, Dv, page):
+        # a query row per (head, map) with zeros where the other map's dims are; both maps' rows come back in float32
+        spread = torch.zeros(N, H, 2, 2, dim, dtype=dtype)
+        qv = q.cpu().view(N, H, 2, dim)
+        spread[:, :, 0, 0], spread[:, :, 1, 1] = qv[:, :, 0], qv[:, :, 1]
+        maps = torch.empty(N, H * 2 * Dv, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops.attention_prefill_tcgen05(None, spread.view(N, H * 4 * dim).to(DEV), k_pool, v_pool, table, i32([0, new[0], N]),
+                                      i32([0, 1]), i32([lens[0] - new[0], lens[1] - new[1]]), 2 * H, scale, status, window,
+                                      keep_first=keep, out_float=maps)
+        out = torch.empty(N, H * Dv, device=DEV, dtype=dtype)
+        ops.diff_combine(out, maps, H, lam, eps, 1.0 - diff)
+        assert int(status.item()) == 0
+        assert part_err(out.double().cpu(), want) < tol
 
 
 def test_table_routing_and_capped_logits():
@@ -189,15 +213,15 @@ def run_part(h, part, x, dtype, sizes, entry=None, ids=None):
 def test_mixers_alone(tmp_path, dtype):
     g = torch.Generator().manual_seed(4)
     for name, layer, entry in (("A", 0, 0), ("A", 0, 5), ("A", 1, 1), ("A", 2, 4), ("B", 0, 0), ("B", 1, 1), ("C", 0, 1),
-                               ("D", 0, 0)):
+                               ("D", 0, 0), ("D", 1, 1), ("D", 0, 2)):
         folder, cfg, w = make_folder(tmp_path, name)
         spec = [l for l in cfg["layers"] if "weights_of" not in l][layer]
         pre = "l%d.mix." % cfg["layers"].index(spec)
-        n = 170 if name in "CD" else 70
+        n = {"C": 170, "D": 300}.get(name, 70)
         x = (torch.randn(n, cfg["width"], generator=g) * 1.5).bfloat16().double()
         want = plain.attention(x, w, pre, spec["mixer"], cfg["norm"]["eps"])
         for sizes in ((n,), (1,), (33, 2, 1, 30, 1)):
-            h = Harness(folder, dtype, max_len=192)
+            h = Harness(folder, dtype, max_len=320)
             got = run_part(h, h.model.layers[layer].mixer, x, dtype, sizes, entry=entry)
             assert part_err(got, want) < PART_TOL[dtype], (name, layer, sizes)
 
