@@ -66,7 +66,7 @@ __device__ __forceinline__ bool sees(int pos, int key, int window, int keep_firs
 }
 
 template <typename T>
-__global__ void __launch_bounds__(THREADS) diff_attention_kernel(DiffArgs a) {
+__global__ void __launch_bounds__(THREADS, 4) diff_attention_kernel(DiffArgs a) {
     sb::pdl_launch_dependents();
     sb::pdl_wait();
     __shared__ float qs[SUBS][DIMMAX];
@@ -74,6 +74,8 @@ __global__ void __launch_bounds__(THREADS) diff_attention_kernel(DiffArgs a) {
     __shared__ float run_max[SUBS], run_sum[SUBS], rescale[SUBS];
     __shared__ int vrow[KEYS];             // the pool row (page, KV head, slot) of every key of the chunk
     __shared__ float red[33];
+    constexpr int VEC = Vec16<T>::N;
+    __shared__ float vred[SUBS][THREADS * VEC];      // [row][row group][value dim] of the 16-byte value path
     const int kh = blockIdx.x, n = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = a.H / a.Hkv, dim = a.dim, Dv = a.Dv, BS = a.BS;
@@ -87,8 +89,14 @@ __global__ void __launch_bounds__(THREADS) diff_attention_kernel(DiffArgs a) {
     const T* q = (const T*)a.q;
     const T* kp = (const T*)a.k_pool;
     const T* vp = (const T*)a.v_pool;
-    constexpr int VEC = Vec16<T>::N;
     const bool vec = dim % VEC == 0 && (reinterpret_cast<uintptr_t>(kp) & 15) == 0;
+    // Values in 16-byte pieces: LPR neighbouring threads read one value row, the block RP rows at a time, and a
+    // thread keeps VEC dims of every row's sum; the row groups are added up (in order) after the last chunk.
+    // Taken when a value row is a power of two of such pieces.
+    const int LPR = Dv / VEC;
+    const bool vvec = Dv % VEC == 0 && LPR <= THREADS && (LPR & (LPR - 1)) == 0 &&
+                      (reinterpret_cast<uintptr_t>(vp) & 15) == 0;
+    const int RP = vvec ? THREADS / LPR : 1, rg = vvec ? tid / LPR : 0, lp = vvec ? tid % LPR : 0;
 
     for (int g0 = 0; g0 < G; g0 += SUBS / 2) {
         const int gn = min(SUBS / 2, G - g0), h0 = kh * G + g0, sn = 2 * gn;
@@ -99,9 +107,12 @@ __global__ void __launch_bounds__(THREADS) diff_attention_kernel(DiffArgs a) {
         }
         for (int i = sn * dim + tid; i < SUBS * dim; i += THREADS) qs[i / dim][i % dim] = 0.f;
         if (tid < SUBS) { run_max[tid] = -INFINITY; run_sum[tid] = 0.f; rescale[tid] = 0.f; }
-        float acc[SUBS][2];
+        // a row's sums: dims tid and tid + THREADS in [0] and [1], or the VEC dims of the 16-byte value path
+        float accv[SUBS][VEC];
 #pragma unroll
-        for (int s = 0; s < SUBS; ++s) acc[s][0] = acc[s][1] = 0.f;
+        for (int s = 0; s < SUBS; ++s)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) accv[s][e] = 0.f;
         __syncthreads();
         for (int c0 = lo; c0 < hi; c0 += KEYS) {
             const int nk = min(KEYS, hi - c0);
@@ -115,7 +126,7 @@ __global__ void __launch_bounds__(THREADS) diff_attention_kernel(DiffArgs a) {
 #pragma unroll
                 for (int s = 0; s < SUBS; ++s) dot[s] = 0.f;
                 if (vec) {
-#pragma unroll 2
+#pragma unroll 4
                     for (int d = 0; d < dim; d += VEC) {
                         Vec16<T> k1, k2;
                         k1.load(kr + d);
@@ -160,8 +171,38 @@ __global__ void __launch_bounds__(THREADS) diff_attention_kernel(DiffArgs a) {
             }
             __syncthreads();
             // weighted sum of the values: thread t owns dims t and t + THREADS; both maps read the same values
+            if (vvec) {
 #pragma unroll
-            for (int s = 0; s < SUBS; ++s) { acc[s][0] *= rescale[s]; acc[s][1] *= rescale[s]; }
+                for (int s = 0; s < SUBS; ++s) {
+                    const float f = rescale[s];
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) accv[s][e] *= f;
+                }
+                for (int t0 = 0; t0 < nk; t0 += 4 * RP) {        // four rows' loads in flight per thread
+                    Vec16<T> x[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int t = t0 + j * RP + rg;
+                        x[j].load(vp + (size_t)vrow[t < nk ? t : 0] * Dv + lp * VEC);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int t = t0 + j * RP + rg;
+                        if (t >= nk) continue;
+#pragma unroll
+                        for (int s = 0; s < SUBS; ++s) {
+                            if (s >= sn) continue;
+                            const float ws = w[s][t];
+#pragma unroll
+                            for (int e = 0; e < VEC; ++e) accv[s][e] = fmaf(ws, x[j].get(e), accv[s][e]);
+                        }
+                    }
+                }
+                __syncthreads();
+                continue;
+            }
+#pragma unroll
+            for (int s = 0; s < SUBS; ++s) { accv[s][0] *= rescale[s]; accv[s][1] *= rescale[s]; }
 #pragma unroll 8
             for (int t = 0; t < nk; ++t) {
                 const T* vr = vp + (size_t)vrow[t] * Dv;
@@ -170,19 +211,37 @@ __global__ void __launch_bounds__(THREADS) diff_attention_kernel(DiffArgs a) {
 #pragma unroll
                 for (int s = 0; s < SUBS; ++s) {
                     if (s >= sn) continue;
-                    acc[s][0] = fmaf(w[s][t], v0, acc[s][0]);
-                    acc[s][1] = fmaf(w[s][t], v1, acc[s][1]);
+                    accv[s][0] = fmaf(w[s][t], v0, accv[s][0]);
+                    accv[s][1] = fmaf(w[s][t], v1, accv[s][1]);
                 }
             }
             __syncthreads();
+        }
+        if (vvec) {
+            // the row groups' sums, added in the order 0, 1, ...: thread t takes dims t and t + THREADS as below
+#pragma unroll
+            for (int s = 0; s < SUBS; ++s)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) vred[s][rg * Dv + lp * VEC + e] = accv[s][e];
+            __syncthreads();
+#pragma unroll
+            for (int s = 0; s < SUBS; ++s) {
+                float s0 = 0.f, s1 = 0.f;
+                for (int r = 0; r < RP; ++r) {
+                    if (tid < Dv) s0 += vred[s][r * Dv + tid];
+                    if (tid + THREADS < Dv) s1 += vred[s][r * Dv + tid + THREADS];
+                }
+                accv[s][0] = s0;
+                accv[s][1] = s1;
+            }
         }
         if (a.NP == 1) {
 #pragma unroll
             for (int g = 0; g < SUBS / 2; ++g) {
                 if (g >= gn) continue;                       // uniform over the block
                 const float f1 = 1.0f / run_sum[2 * g], f2 = a.lambda / run_sum[2 * g + 1];
-                const float o0 = tid < Dv ? acc[2 * g][0] * f1 - acc[2 * g + 1][0] * f2 : 0.f;
-                const float o1 = tid + THREADS < Dv ? acc[2 * g][1] * f1 - acc[2 * g + 1][1] * f2 : 0.f;
+                const float o0 = tid < Dv ? accv[2 * g][0] * f1 - accv[2 * g + 1][0] * f2 : 0.f;
+                const float o1 = tid + THREADS < Dv ? accv[2 * g][1] * f1 - accv[2 * g + 1][1] * f2 : 0.f;
                 const float ss = block_sum(o0 * o0 + o1 * o1, red);
                 const float r = a.out_scale / sqrtf(ss / (float)Dv + a.eps);
                 T* o = (T*)a.out + ((size_t)n * a.H + h0 + g) * Dv;
@@ -195,8 +254,8 @@ __global__ void __launch_bounds__(THREADS) diff_attention_kernel(DiffArgs a) {
                 if (s >= sn) continue;
                 const size_t slot = (((size_t)n * a.H + h0) * 2 + s) * a.NP + blockIdx.z;
                 float* o = a.part_o + slot * Dv;
-                if (tid < Dv) o[tid] = acc[s][0];
-                if (tid + THREADS < Dv) o[tid + THREADS] = acc[s][1];
+                if (tid < Dv) o[tid] = accv[s][0];
+                if (tid + THREADS < Dv) o[tid + THREADS] = accv[s][1];
                 if (tid == 0) {                              // an empty share has sum 0 and is skipped by the merge
                     a.part_ml[slot * 2] = run_max[s];
                     a.part_ml[slot * 2 + 1] = run_sum[s];

@@ -242,7 +242,8 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
 }
 
 // ----------------------------------------------------------------------------------------
-// Per-head QK-RMSNorm, rotation and paged KV write, one warp per (token, head).
+// Per-head QK-RMSNorm, rotation and paged KV write: a block per token and `hpb` heads, a warp per head at a time
+// (the token's cosines and sines are made once per block; a lane's loads of a head are issued together).
 //   heads 0..Hq-1        : q  -> norm(q_gain) -> rotate -> q_out[n, h, :]
 //   heads Hq..Hq+Hkv-1   : k  -> norm(k_gain) -> rotate -> k_pool[page, kh, off, :]
 //   heads Hq+Hkv..       : v  ->                           v_pool[page, kh, off, :]
@@ -266,77 +267,104 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     const float* __restrict__ inv_freq, int R, const int* __restrict__ positions,
     const int* __restrict__ token_rows, const int* __restrict__ block_table, int table_width,
     int BS, float eps, int Hq, int Hkv, int D, int write_kv, int Dv, int row_width, int neighbours,
-    const float* __restrict__ bias, int sub, float magnitude, int spread) {
+    const float* __restrict__ bias, int sub, float magnitude, int spread, int hpb) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     __shared__ float buf[4][256];
+    __shared__ float cs[2][128];     // the token's cosines and sines (times `magnitude`), shared by its heads
     const int n = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.y * 4 + warp;
     const int n_heads = Hq + 2 * Hkv;
-    if (head >= n_heads) return;
-    const bool is_q = head < Hq;
-    const bool is_k = !is_q && head < Hq + Hkv;
-    const bool is_v = !is_q && !is_k;
-    if (!is_q && !write_kv) return;
-
-    // a row holds Hq + Hkv heads of D dims, then Hkv value heads of Dv dims (and whatever follows them)
-    const int Dh = is_v ? Dv : D;
-    const size_t base = (size_t)n * row_width + (is_v ? (size_t)(Hq + Hkv) * D + (size_t)(head - Hq - Hkv) * Dv
-                                                       : (size_t)head * D);
-    float* y = buf[warp];
-    float ss = 0.f;
-    for (int i = lane; i < Dh; i += 32) {
-        float v;
-        if (parts != nullptr) {
-            v = 0.f;
-            for (int s = 0; s < S; ++s) v += parts[s * part_stride + base + i];
-        } else {
-            v = to_float(qkv[base + i]);
-        }
-        if (bias != nullptr) v += bias[base - (size_t)n * row_width + i];
-        y[i] = v;
-        ss += v * v;
-    }
     const int pos = positions[n];
-    const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
-    if (gain != nullptr) {
-        ss = warp_sum(ss);
-        const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
-        for (int i = lane; i < D; i += 32) y[i] = y[i] * rinv * gain[i];
-    }
-    __syncwarp();
-
-    T* dst;
-    const int maps = D / sub;
-    if (is_q) {
-        dst = q_out + ((size_t)n * Hq + head) * D * (spread ? maps : 1);
-    } else {
-        const int kh = is_k ? head - Hq : head - Hq - Hkv;
-        const int row = token_rows[n];
-        const int page = block_table[(size_t)row * table_width + pos / BS];
-        T* pool = is_k ? k_pool : v_pool;
-        dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * Dh;
-    }
     const int half = R >> 1;
-    for (int i = lane; i < Dh; i += 32) {
-        float o = y[i];
-        const int ii = i % sub;          // a head of several maps: every `sub` dims rotate on their own
-        if (!is_v && ii < R) {
-            // the partner of dim i and the frequency they share: halves (j, j + R/2) or neighbours (2j, 2j+1)
-            const bool first = neighbours ? (ii & 1) == 0 : ii < half;
-            const int j = neighbours ? ii >> 1 : (first ? ii : ii - half);
-            const int mate = neighbours ? (i ^ 1) : (first ? i + half : i - half);
-            const float ang = (float)pos * inv_freq[j];
-            const float c = cosf(ang) * magnitude, s = sinf(ang) * magnitude;
-            o = first ? y[i] * c - y[mate] * s : y[i] * c + y[mate] * s;
-        }
-        if (is_q && spread) {
-            // a row per map: the map's dims in their place, zeros where the other maps' dims are
-            for (int m = 0; m < maps; ++m) dst[(size_t)m * D + i] = from_float<T>(m == i / sub ? o : 0.f);
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float ang = (float)pos * inv_freq[j];
+        cs[0][j] = cosf(ang) * magnitude;
+        cs[1][j] = sinf(ang) * magnitude;
+    }
+    __syncthreads();
+    const int head_end = min(n_heads, ((int)blockIdx.y + 1) * hpb);
+    const int maps = D / sub;
+    float* y = buf[warp];
+    for (int head = blockIdx.y * hpb + warp; head < head_end; head += 4) {
+        const bool is_q = head < Hq;
+        const bool is_k = !is_q && head < Hq + Hkv;
+        const bool is_v = !is_q && !is_k;
+        if (!is_q && !write_kv) break;
+
+        // a row holds Hq + Hkv heads of D dims, then Hkv value heads of Dv dims (and whatever follows them)
+        const int Dh = is_v ? Dv : D;
+        const size_t col = is_v ? (size_t)(Hq + Hkv) * D + (size_t)(head - Hq - Hkv) * Dv : (size_t)head * D;
+        const size_t base = (size_t)n * row_width + col;
+        // lane l owns dims l, l + 32, ...: the loads of all of them are issued before any is used
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = 0.f;
+        if (parts != nullptr) {
+            for (int s = 0; s < S; ++s) {
+                float t[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = lane + 32 * u;
+                    t[u] = i < Dh ? parts[s * part_stride + base + i] : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] += t[u];
+            }
         } else {
-            dst[i] = from_float<T>(o);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = lane + 32 * u;
+                if (i < Dh) v[u] = to_float(qkv[base + i]);
+            }
         }
+        float ss = 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = lane + 32 * u;
+            if (i < Dh) {
+                if (bias != nullptr) v[u] += bias[col + i];
+                y[i] = v[u];
+                ss += v[u] * v[u];
+            }
+        }
+        const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
+        if (gain != nullptr) {
+            ss = warp_sum(ss);
+            const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
+            for (int i = lane; i < D; i += 32) y[i] = y[i] * rinv * gain[i];
+        }
+        __syncwarp();
+
+        T* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)n * Hq + head) * D * (spread ? maps : 1);
+        } else {
+            const int kh = is_k ? head - Hq : head - Hq - Hkv;
+            const int row = token_rows[n];
+            const int page = block_table[(size_t)row * table_width + pos / BS];
+            T* pool = is_k ? k_pool : v_pool;
+            dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * Dh;
+        }
+        for (int i = lane; i < Dh; i += 32) {
+            float o = y[i];
+            const int ii = i % sub;          // a head of several maps: every `sub` dims rotate on their own
+            if (!is_v && ii < R) {
+                // the partner of dim i and the frequency they share: halves (j, j + R/2) or neighbours (2j, 2j+1)
+                const bool first = neighbours ? (ii & 1) == 0 : ii < half;
+                const int j = neighbours ? ii >> 1 : (first ? ii : ii - half);
+                const int mate = neighbours ? (i ^ 1) : (first ? i + half : i - half);
+                const float c = cs[0][j], s = cs[1][j];
+                o = first ? y[i] * c - y[mate] * s : y[i] * c + y[mate] * s;
+            }
+            if (is_q && spread) {
+                // a row per map: the map's dims in their place, zeros where the other maps' dims are
+                for (int m = 0; m < maps; ++m) dst[(size_t)m * D + i] = from_float<T>(m == i / sub ? o : 0.f);
+            } else {
+                dst[i] = from_float<T>(o);
+            }
+        }
+        __syncwarp();                        // the next head of this warp overwrites y
     }
 }
 
@@ -570,7 +598,7 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
                       magnitude == 1.0f && !spread;
     // Heads per block: 4 (a head per warp) while that still fills the GPU, more for long batches.
     int hpb = 4;
-    if (fast) {
+    {
         const long long blocks_wanted = 148LL * 8;
         hpb = (int)(((long long)N * n_heads + blocks_wanted - 1) / blocks_wanted);
         hpb = ((hpb + 3) / 4) * 4;
@@ -592,7 +620,7 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
     else if (fast) { SB_QK_FAST(8) }
 #undef SB_QK_FAST
     else sb::launch(qk_norm_rope_kvwrite_kernel<T>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, D, write_kv, Dv,
-                    row_width, neighbours, bias, sub, magnitude, spread);
+                    row_width, neighbours, bias, sub, magnitude, spread, hpb);
 #undef SB_QK_ARGS
 }
 
