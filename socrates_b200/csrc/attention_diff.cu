@@ -69,13 +69,13 @@ template <typename T>
 __global__ void __launch_bounds__(THREADS, 4) diff_attention_kernel(DiffArgs a) {
     sb::pdl_launch_dependents();
     sb::pdl_wait();
-    __shared__ float qs[SUBS][DIMMAX];
+    __shared__ __align__(16) float qs[SUBS][DIMMAX];
     __shared__ float w[SUBS][KEYS];
     __shared__ float run_max[SUBS], run_sum[SUBS], rescale[SUBS];
     __shared__ int vrow[KEYS];             // the pool row (page, KV head, slot) of every key of the chunk
     __shared__ float red[33];
     constexpr int VEC = Vec16<T>::N;
-    __shared__ float vred[SUBS][THREADS * VEC];      // [row][row group][value dim] of the 16-byte value path
+    __shared__ __align__(16) float vred[SUBS][THREADS * VEC];      // [row][row group][value dim] of the 16-byte value path
     const int kh = blockIdx.x, n = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = a.H / a.Hkv, dim = a.dim, Dv = a.Dv, BS = a.BS;
@@ -132,10 +132,18 @@ __global__ void __launch_bounds__(THREADS, 4) diff_attention_kernel(DiffArgs a) 
                         k1.load(kr + d);
                         k2.load(kr + dim + d);
 #pragma unroll
-                        for (int e = 0; e < VEC; ++e) {
-                            const float f1 = k1.get(e), f2 = k2.get(e);
+                        for (int e = 0; e < VEC; e += 4) {
+                            const float f1[4] = {k1.get(e), k1.get(e + 1), k1.get(e + 2), k1.get(e + 3)};
+                            const float f2[4] = {k2.get(e), k2.get(e + 1), k2.get(e + 2), k2.get(e + 3)};
 #pragma unroll
-                            for (int s = 0; s < SUBS; ++s) dot[s] = fmaf(qs[s][d + e], (s & 1) ? f2 : f1, dot[s]);
+                            for (int s = 0; s < SUBS; ++s) {
+                                const float4 qv = *reinterpret_cast<const float4*>(&qs[s][d + e]);
+                                const float* f = (s & 1) ? f2 : f1;
+                                dot[s] = fmaf(qv.x, f[0], dot[s]);
+                                dot[s] = fmaf(qv.y, f[1], dot[s]);
+                                dot[s] = fmaf(qv.z, f[2], dot[s]);
+                                dot[s] = fmaf(qv.w, f[3], dot[s]);
+                            }
                         }
                     }
                 } else {
@@ -190,8 +198,7 @@ __global__ void __launch_bounds__(THREADS, 4) diff_attention_kernel(DiffArgs a) 
                         const int t = t0 + j * RP + rg;
                         if (t >= nk) continue;
 #pragma unroll
-                        for (int s = 0; s < SUBS; ++s) {
-                            if (s >= sn) continue;
+                        for (int s = 0; s < SUBS; ++s) {         // rows beyond the pass's heads have weight 0
                             const float ws = w[s][t];
 #pragma unroll
                             for (int e = 0; e < VEC; ++e) accv[s][e] = fmaf(ws, x[j].get(e), accv[s][e]);
@@ -222,16 +229,20 @@ __global__ void __launch_bounds__(THREADS, 4) diff_attention_kernel(DiffArgs a) 
 #pragma unroll
             for (int s = 0; s < SUBS; ++s)
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) vred[s][rg * Dv + lp * VEC + e] = accv[s][e];
+                for (int e = 0; e < VEC; e += 4)
+                    *reinterpret_cast<float4*>(&vred[s][rg * Dv + lp * VEC + e]) =
+                        make_float4(accv[s][e], accv[s][e + 1], accv[s][e + 2], accv[s][e + 3]);
             __syncthreads();
+            const int d0 = tid < Dv ? tid : 0, d1 = tid + THREADS < Dv ? tid + THREADS : d0;
 #pragma unroll
             for (int s = 0; s < SUBS; ++s) {
                 float s0 = 0.f, s1 = 0.f;
+#pragma unroll 4
                 for (int r = 0; r < RP; ++r) {
-                    if (tid < Dv) s0 += vred[s][r * Dv + tid];
-                    if (tid + THREADS < Dv) s1 += vred[s][r * Dv + tid + THREADS];
+                    s0 += vred[s][r * Dv + d0];
+                    if (Dv > THREADS) s1 += vred[s][r * Dv + d1];
                 }
-                accv[s][0] = s0;
+                accv[s][0] = s0;                              // threads beyond Dv hold a copy that nothing reads
                 accv[s][1] = s1;
             }
         }

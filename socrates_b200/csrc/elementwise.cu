@@ -260,7 +260,7 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
 // rotated dims); dims that do not rotate are not scaled.  With `spread` the queries are written one
 // row per (head, map), [N, Hq * maps, D]: the map's dims where they are and zeros elsewhere.
 template <typename T>
-__global__ void qk_norm_rope_kvwrite_kernel(
+__global__ void __launch_bounds__(128, 6) qk_norm_rope_kvwrite_kernel(
     const T* __restrict__ qkv, const float* __restrict__ parts, int S, size_t part_stride,
     T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
     const float* __restrict__ q_gain, const float* __restrict__ k_gain,
@@ -277,6 +277,8 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     const int n_heads = Hq + 2 * Hkv;
     const int pos = positions[n];
     const int half = R >> 1;
+    // the token's page: looked up before anything else so that its two dependent loads overlap the rest
+    const int page = write_kv ? block_table[(size_t)token_rows[n] * table_width + pos / BS] : 0;
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
         const float ang = (float)pos * inv_freq[j];
         cs[0][j] = cosf(ang) * magnitude;
@@ -286,6 +288,28 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     const int head_end = min(n_heads, ((int)blockIdx.y + 1) * hpb);
     const int maps = D / sub;
     float* y = buf[warp];
+    // What a lane needs to rotate its dims i = lane + 32u is the same for every query and key head: the dim's
+    // partner, its cosine and its signed sine (o_i = y_i c + y_mate s'), and the map it belongs to.  A dim that
+    // does not rotate is its own partner with c = 1 and s' = 0.
+    float rc[8], rs[8];
+    int rmate[8], rmap[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = lane + 32 * u;
+        const int ii = i % sub;              // a head of several maps: every `sub` dims rotate on their own
+        rc[u] = 1.f;
+        rs[u] = 0.f;
+        rmate[u] = i;
+        rmap[u] = i / sub;
+        if (i < D && ii < R) {
+            // the partner of dim i and the frequency they share: halves (j, j + R/2) or neighbours (2j, 2j+1)
+            const bool first = neighbours ? (ii & 1) == 0 : ii < half;
+            const int j = neighbours ? ii >> 1 : (first ? ii : ii - half);
+            rmate[u] = neighbours ? (i ^ 1) : (first ? i + half : i - half);
+            rc[u] = cs[0][j];
+            rs[u] = first ? -cs[1][j] : cs[1][j];
+        }
+    }
     for (int head = blockIdx.y * hpb + warp; head < head_end; head += 4) {
         const bool is_q = head < Hq;
         const bool is_k = !is_q && head < Hq + Hkv;
@@ -297,19 +321,27 @@ __global__ void qk_norm_rope_kvwrite_kernel(
         const size_t col = is_v ? (size_t)(Hq + Hkv) * D + (size_t)(head - Hq - Hkv) * Dv : (size_t)head * D;
         const size_t base = (size_t)n * row_width + col;
         // lane l owns dims l, l + 32, ...: the loads of all of them are issued before any is used
-        float v[8];
+        float v[8], b[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = 0.f;
+        for (int u = 0; u < 8; ++u) {
+            const int i = lane + 32 * u;
+            v[u] = 0.f;
+            b[u] = (bias != nullptr && i < Dh) ? bias[col + i] : 0.f;
+        }
         if (parts != nullptr) {
-            for (int s = 0; s < S; ++s) {
-                float t[8];
+            for (int s = 0; s < S; s += 2) {                 // two splits' loads in flight; added in the order s, s + 1
+                float t[8], t2[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const int i = lane + 32 * u;
                     t[u] = i < Dh ? parts[s * part_stride + base + i] : 0.f;
+                    t2[u] = (i < Dh && s + 1 < S) ? parts[(s + 1) * part_stride + base + i] : 0.f;
                 }
 #pragma unroll
-                for (int u = 0; u < 8; ++u) v[u] += t[u];
+                for (int u = 0; u < 8; ++u) {
+                    v[u] += t[u];
+                    if (s + 1 < S) v[u] += t2[u];
+                }
             }
         } else {
 #pragma unroll
@@ -323,7 +355,7 @@ __global__ void qk_norm_rope_kvwrite_kernel(
         for (int u = 0; u < 8; ++u) {
             const int i = lane + 32 * u;
             if (i < Dh) {
-                if (bias != nullptr) v[u] += bias[col + i];
+                if (bias != nullptr) v[u] += b[u];
                 y[i] = v[u];
                 ss += v[u] * v[u];
             }
@@ -341,25 +373,17 @@ __global__ void qk_norm_rope_kvwrite_kernel(
             dst = q_out + ((size_t)n * Hq + head) * D * (spread ? maps : 1);
         } else {
             const int kh = is_k ? head - Hq : head - Hq - Hkv;
-            const int row = token_rows[n];
-            const int page = block_table[(size_t)row * table_width + pos / BS];
             T* pool = is_k ? k_pool : v_pool;
             dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * Dh;
         }
-        for (int i = lane; i < Dh; i += 32) {
-            float o = y[i];
-            const int ii = i % sub;          // a head of several maps: every `sub` dims rotate on their own
-            if (!is_v && ii < R) {
-                // the partner of dim i and the frequency they share: halves (j, j + R/2) or neighbours (2j, 2j+1)
-                const bool first = neighbours ? (ii & 1) == 0 : ii < half;
-                const int j = neighbours ? ii >> 1 : (first ? ii : ii - half);
-                const int mate = neighbours ? (i ^ 1) : (first ? i + half : i - half);
-                const float c = cs[0][j], s = cs[1][j];
-                o = first ? y[i] * c - y[mate] * s : y[i] * c + y[mate] * s;
-            }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = lane + 32 * u;
+            if (i >= Dh) break;
+            const float o = is_v ? y[i] : y[i] * rc[u] + y[rmate[u]] * rs[u];
             if (is_q && spread) {
                 // a row per map: the map's dims in their place, zeros where the other maps' dims are
-                for (int m = 0; m < maps; ++m) dst[(size_t)m * D + i] = from_float<T>(m == i / sub ? o : 0.f);
+                for (int m = 0; m < maps; ++m) dst[(size_t)m * D + i] = from_float<T>(m == rmap[u] ? o : 0.f);
             } else {
                 dst[i] = from_float<T>(o);
             }
