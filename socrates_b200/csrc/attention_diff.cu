@@ -287,37 +287,43 @@ __global__ void __launch_bounds__(THREADS) diff_merge_kernel(T* __restrict__ out
     __shared__ float red[33];
     const int h = blockIdx.x, n = blockIdx.y, tid = threadIdx.x;
     float a[2][2];                           // [map][dims tid, tid + THREADS]
-    // Loads go out eight at a time and none depends on another's value, so a merge costs a few round trips to
-    // L2 however many shares there are.
+    // Loads go out sixteen shares at a time (both maps' maxima and sums together) and none depends on another's
+    // value, so a merge costs a few round trips to L2 however many shares there are.
+    constexpr int B = 16;
+    const size_t base0 = ((size_t)n * H + h) * 2 * NP;
+    const float2* ml = reinterpret_cast<const float2*>(part_ml) + base0;       // [map][share]
+    float M[2] = {-INFINITY, -INFINITY};
+    for (int p0 = 0; p0 < NP; p0 += B) {
+        float2 v[2][B];
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+            for (int j = 0; j < B; ++j) v[m][j] = p0 + j < NP ? ml[m * NP + p0 + j] : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+            for (int j = 0; j < B; ++j)
+                if (v[m][j].y > 0.f) M[m] = fmaxf(M[m], v[m][j].x);
+    }
+    const bool wide = Dv > THREADS;
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
-        const size_t base = (((size_t)n * H + h) * 2 + m) * NP;
-        const float2* ml = reinterpret_cast<const float2*>(part_ml) + base;
-        float M = -INFINITY;
-        for (int p0 = 0; p0 < NP; p0 += 8) {
-            float2 v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = p0 + j < NP ? ml[p0 + j] : make_float2(0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (v[j].y > 0.f) M = fmaxf(M, v[j].x);
-        }
         float L = 0.f, o0 = 0.f, o1 = 0.f;
-        for (int p0 = 0; p0 < NP; p0 += 8) {
-            float2 v[8];
-            float x0[8], x1[8];
+        for (int p0 = 0; p0 < NP; p0 += B) {
+            float2 v[B];
+            float x0[B], x1[B];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = p0 + j < NP ? ml[p0 + j] : make_float2(0.f, 0.f);   // in L1 by now
+            for (int j = 0; j < B; ++j) v[j] = p0 + j < NP ? ml[m * NP + p0 + j] : make_float2(0.f, 0.f);   // in L1 by now
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float* po = part_o + (base + p0 + j) * Dv;
+            for (int j = 0; j < B; ++j) {
+                const float* po = part_o + (base0 + (size_t)m * NP + p0 + j) * Dv;
                 x0[j] = (v[j].y > 0.f && tid < Dv) ? po[tid] : 0.f;                      // an empty share is never read
-                x1[j] = (v[j].y > 0.f && tid + THREADS < Dv) ? po[tid + THREADS] : 0.f;
+                x1[j] = (wide && v[j].y > 0.f && tid + THREADS < Dv) ? po[tid + THREADS] : 0.f;
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < B; ++j)
                 if (v[j].y > 0.f) {
-                    const float wgt = expf(v[j].x - M);
+                    const float wgt = expf(v[j].x - M[m]);
                     L += wgt * v[j].y;
                     o0 += wgt * x0[j];
                     o1 += wgt * x1[j];

@@ -293,6 +293,7 @@ __global__ void __launch_bounds__(128, 6) qk_norm_rope_kvwrite_kernel(
     // does not rotate is its own partner with c = 1 and s' = 0.
     float rc[8], rs[8];
     int rmate[8], rmap[8];
+    const int nu = (max(D, Dv) + 31) >> 5;      // slots of 32 dims that a head can fill (uniform: the loops stop there)
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         const int i = lane + 32 * u;
@@ -326,7 +327,8 @@ __global__ void __launch_bounds__(128, 6) qk_norm_rope_kvwrite_kernel(
         for (int u = 0; u < 8; ++u) {
             const int i = lane + 32 * u;
             v[u] = 0.f;
-            b[u] = (bias != nullptr && i < Dh) ? bias[col + i] : 0.f;
+            b[u] = 0.f;
+            if (u < nu) b[u] = (bias != nullptr && i < Dh) ? bias[col + i] : 0.f;
         }
         if (parts != nullptr) {
             for (int s = 0; s < S; s += 2) {                 // two splits' loads in flight; added in the order s, s + 1
@@ -334,11 +336,15 @@ __global__ void __launch_bounds__(128, 6) qk_norm_rope_kvwrite_kernel(
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const int i = lane + 32 * u;
-                    t[u] = i < Dh ? parts[s * part_stride + base + i] : 0.f;
-                    t2[u] = (i < Dh && s + 1 < S) ? parts[(s + 1) * part_stride + base + i] : 0.f;
+                    t[u] = t2[u] = 0.f;
+                    if (u < nu) {
+                        t[u] = i < Dh ? parts[s * part_stride + base + i] : 0.f;
+                        t2[u] = (i < Dh && s + 1 < S) ? parts[(s + 1) * part_stride + base + i] : 0.f;
+                    }
                 }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
+                    if (u >= nu) break;
                     v[u] += t[u];
                     if (s + 1 < S) v[u] += t2[u];
                 }
@@ -347,13 +353,14 @@ __global__ void __launch_bounds__(128, 6) qk_norm_rope_kvwrite_kernel(
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const int i = lane + 32 * u;
-                if (i < Dh) v[u] = to_float(qkv[base + i]);
+                if (u < nu && i < Dh) v[u] = to_float(qkv[base + i]);
             }
         }
         float ss = 0.f;
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const int i = lane + 32 * u;
+            if (u >= nu) break;
             if (i < Dh) {
                 if (bias != nullptr) v[u] += b[u];
                 y[i] = v[u];
@@ -381,8 +388,11 @@ __global__ void __launch_bounds__(128, 6) qk_norm_rope_kvwrite_kernel(
             const int i = lane + 32 * u;
             if (i >= Dh) break;
             const float o = is_v ? y[i] : y[i] * rc[u] + y[rmate[u]] * rs[u];
-            if (is_q && spread) {
-                // a row per map: the map's dims in their place, zeros where the other maps' dims are
+            if (is_q && spread && maps == 2) {
+                // a row per map: the map's dims in their place, zeros where the other map's dims are
+                dst[i] = from_float<T>(rmap[u] == 0 ? o : 0.f);
+                dst[D + i] = from_float<T>(rmap[u] == 1 ? o : 0.f);
+            } else if (is_q && spread) {
                 for (int m = 0; m < maps; ++m) dst[(size_t)m * D + i] = from_float<T>(m == rmap[u] ? o : 0.f);
             } else {
                 dst[i] = from_float<T>(o);
