@@ -608,7 +608,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--compare", default=None, choices=("bofusun", "loletar", "samerax"),
-                    help="the Bofusun or the Loletar design at real layer widths beside Qwen3 at equal size "
+                    help="the Bofusun, the Loletar or the Samerax design at real layer widths beside Qwen3 at equal size "
                          "(prefill and decode); the default workload is not run")
     ap.add_argument("--only", default=None, help="with --compare: run only these of the pair, e.g. 'loletar' or 'qwen3'")
     ap.add_argument("--sizes", default=None, help="with --compare: widths to run, of 1k,2k,4k (default 1k,2k)")
