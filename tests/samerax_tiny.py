@@ -7,7 +7,7 @@ bfloat16 engine serves on the tensor cores), full, partial
 and no rotation, with and without stretched frequencies, windows shorter than a page, longer than a
 chunk of 128 keys and absent, kept first keys of 0, 1, a whole page and more than the window, dense,
 routed and no feed-forwards, top-1, top = every expert, layers that run an earlier layer's weights
-(next to it and further on), logits with and without a cap.
+(next to it and further on), logits with and without a cap, and one model whose sizes are no multiple of 8.
 """
 
 from __future__ import annotations
@@ -50,6 +50,9 @@ _C0 = _att(4, 2, 64, 32, 0.15, 0.45, rot=32, base=50000.0, scaling=(8.0, 64, 4.0
 _D0 = _att(2, 1, 64, 128, 0.1, 0.25, rot=64, base=1000.0, size=100, keep=65)
 _D1 = _att(6, 3, 32, 64, 0.2, 0.4, rot=8, base=100.0, scaling=(2.0, 16, 4.0, 1.0), size=70, keep=9)
 
+_E0 = _att(3, 1, 6, 10, 0.4, 0.35, rot=4, base=1000.0, scaling=(3.0, 24, 6.0, 1.0), size=21, keep=3)
+_E1 = _att(2, 2, 10, 6, 0.3, 0.55, rot=10, base=300.0, size=50, keep=7)
+
 TINY = {
     # three query heads a group, partial stretched rotation, a window with a few kept keys; layers run again
     # (next to their owner and later); a layer without a feed-forward; maps of 12 dims (no 16-byte rows in bfloat16)
@@ -73,6 +76,10 @@ TINY = {
     # the tensor-core attention kernel; kept keys that fill a key tile of 64 and one more, and a few only
     "D": {"architecture": "Samerax", "vocab": 80, "width": 96, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0},
           "logit_softcap": 50.0, "layers": [_layer(_D0, _dense(64)), _layer(_D1, _moe(24, 3, 2)), _layer(_D0, _dense(64), 0)]},
+    # a width, feed-forwards, maps and values that are no multiple of 8 (no 16-byte rows anywhere in bfloat16), an odd
+    # vocabulary, three of seven experts
+    "E": {"architecture": "Samerax", "vocab": 53, "width": 36, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.5},
+          "logit_softcap": 12.0, "layers": [_layer(_E0, _dense(20)), _layer(_E1, _moe(12, 7, 3)), _layer(_E0, _dense(20), 0)]},
 }
 
 

@@ -243,7 +243,7 @@ def test_feed_forwards_alone(tmp_path, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_stream_after_every_layer(tmp_path, dtype, name):
     import socrates_b200.engine.context as C
     from socrates_b200.parts.norm import fold_and_norm
@@ -287,7 +287,7 @@ def models(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_prompts_decoding_and_portions(models, dtype, name):
     folder, cfg, w, seqs, want = models[name]
     h = Harness(folder, dtype)
@@ -308,7 +308,7 @@ def test_whole_prompts_decoding_and_portions(models, dtype, name):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_unequal_requests_in_one_batch(models, dtype, name):
     """Four requests of 150, 23, 77 and 4 tokens: portions of some beside single tokens of others, a
     request that joins late and one that sits steps out; each must come out as it does alone."""
