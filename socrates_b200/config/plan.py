@@ -40,6 +40,8 @@ class LayerSpec:
     norms: Tuple[PartSpec, ...]
     mixer: PartSpec
     feed_forward: Optional[PartSpec]      # None: the layer has a mixer only
+    # Sizes and constants of the arrangement itself (how many residual streams, a factor on every branch).
+    params: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

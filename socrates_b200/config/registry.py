@@ -13,6 +13,7 @@ from typing import Any, Dict, Mapping
 
 from .bofusun import BofusunConfig
 from .loletar import LoletarConfig
+from .magedra import MagedraConfig
 from .qwen3 import ConfigError, Qwen3Config
 from .samerax import SameraxConfig
 
@@ -61,3 +62,4 @@ register_architecture(Qwen3Config.architecture, Qwen3Config)
 register_architecture(BofusunConfig.architecture, BofusunConfig)
 register_architecture(LoletarConfig.architecture, LoletarConfig)
 register_architecture(SameraxConfig.architecture, SameraxConfig)
+register_architecture(MagedraConfig.architecture, MagedraConfig)

@@ -1,0 +1,176 @@
+// The residual as several streams (hyper-connections), folded and normed in one pass.
+//
+// A row holds `s` streams x_1 .. x_s of d floats (s = 1: the ordinary residual).  A sublayer reads
+// u = sum_t in[t] x_t, and its output y joins all streams at once:
+//     x_t <- sum_f mix[f][t] x_f + mult * outw[t] * y
+// The kernel does, per row, whatever of this is waiting, then norms the next reading:
+//     y   = scale_a * (sum_p A[p] + bias) + scale_b * sum_p B[p]      (two branches' partial sums, B optional)
+//     x_t <- sum_f mix[f][t] x_f + mult * outw[t] * y                 (mix null: identity; outw null: ones)
+//     u   = sum_t in[t] x_t                                           (in null: ones, the plain sum)
+//     out = (u - mean(u)) / sqrt(mean((u - mean)^2) + eps) * gain     (center = 1: layer norm)
+//     out = u / sqrt(mean(u^2) + eps) * gain                          (center = 0: RMS norm)
+//     out = u                                                         (gain null)
+// With `init` the streams do not exist yet: every x_t starts as init[row].  With `row_index` only
+// the named rows are read and nothing is written back (the rows whose logits are wanted).
+// Everything is float32; the variance is taken over the deviations in a second pass over the row,
+// which sits in shared memory.
+#include <math.h>
+
+#include "common.cuh"
+
+using namespace sb;
+
+namespace {
+
+constexpr int SMAX = 8;
+
+struct HyperArgs {
+    float* streams;            // [rows, s, d]
+    const float* init;         // [rows, d] or null
+    const float* a; int SA; size_t stride_a; float scale_a;
+    const float* b; int SB; size_t stride_b; float scale_b;
+    const float* bias;         // [d] or null
+    const float* mix;          // [s, s] (from, to) or null
+    const float* outw;         // [s] or null
+    const float* inw;          // [s] or null
+    const float* gain;         // [d] or null
+    float mult, eps;
+    int center;
+    void* out;                 // [M, d] or null
+    float* read_out;           // [M, d] float32 or null: u itself
+    const int* row_index;
+    int s, d, write_streams, has_branch;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) hyper_fold_norm_kernel(HyperArgs a) {
+    sb::pdl_launch_dependents();
+    extern __shared__ float urow[];         // d floats
+    __shared__ float scratch[33];
+    __shared__ float c_mix[SMAX * SMAX], c_out[SMAX], c_in[SMAX];
+    const int s = a.s, d = a.d, m = blockIdx.x;
+    // constants of the model: they may be read before the kernel before this one has finished
+    for (int i = threadIdx.x; i < s * s; i += blockDim.x) c_mix[i] = a.mix ? a.mix[i] : (i / s == i % s ? 1.f : 0.f);
+    for (int i = threadIdx.x; i < s; i += blockDim.x) {
+        c_out[i] = (a.outw ? a.outw[i] : 1.f) * a.mult;
+        c_in[i] = a.inw ? a.inw[i] : 1.f;
+    }
+    sb::pdl_wait();
+    __syncthreads();
+    const int r = a.row_index ? a.row_index[m] : m;
+    float* xs = a.streams + (size_t)r * s * d;
+    float total = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float x[SMAX];
+        if (a.init) {
+            const float v = a.init[(size_t)r * d + i];
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t) x[t] = v;
+        } else {
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t) x[t] = t < s ? xs[(size_t)t * d + i] : 0.f;
+        }
+        if (a.has_branch) {
+            float ya = 0.f, yb = 0.f;
+            for (int p0 = 0; p0 < a.SA; p0 += 8) {                 // eight loads in flight, added in order
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (p0 + j < a.SA) v[j] = __ldg(a.a + (size_t)(p0 + j) * a.stride_a + (size_t)r * d + i);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (p0 + j < a.SA) ya += v[j];
+            }
+            if (a.bias) ya += a.bias[i];
+            for (int p0 = 0; p0 < a.SB; p0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (p0 + j < a.SB) v[j] = __ldg(a.b + (size_t)(p0 + j) * a.stride_b + (size_t)r * d + i);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (p0 + j < a.SB) yb += v[j];
+            }
+            const float y = a.SB > 0 ? a.scale_a * ya + a.scale_b * yb : a.scale_a * ya;
+            float nx[SMAX];
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t) {
+                float v = 0.f;
+                if (t < s) {
+#pragma unroll
+                    for (int f = 0; f < SMAX; ++f)
+                        if (f < s) v = fmaf(c_mix[f * s + t], x[f], v);
+                    v = fmaf(c_out[t], y, v);
+                }
+                nx[t] = v;
+            }
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t) x[t] = nx[t];
+        }
+        if (a.write_streams) {
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t)
+                if (t < s) xs[(size_t)t * d + i] = x[t];
+        }
+        float u = 0.f;
+#pragma unroll
+        for (int t = 0; t < SMAX; ++t)
+            if (t < s) u = fmaf(c_in[t], x[t], u);
+        urow[i] = u;
+        total += u;
+        if (a.read_out) a.read_out[(size_t)m * d + i] = u;
+    }
+    if (a.out == nullptr) return;
+    T* o = (T*)a.out + (size_t)m * d;
+    if (a.gain == nullptr) {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<T>(urow[i]);
+        return;
+    }
+    float mean = 0.f;
+    if (a.center) mean = block_sum(total, scratch) / (float)d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = urow[i] - mean;
+        ss += v * v;
+    }
+    const float var = block_sum(ss, scratch) / (float)d;
+    const float rinv = 1.0f / sqrtf(var + a.eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<T>((urow[i] - mean) * rinv * a.gain[i]);
+}
+
+}  // namespace
+
+extern "C" int sb_hyper_fold_norm(float* streams, const float* init, int s, int d, const float* a, int SA,
+                                  long long stride_a, float scale_a, const float* b, int SB, long long stride_b,
+                                  float scale_b, const float* bias, const float* mix, const float* outw, float mult,
+                                  const float* inw, const float* gain, float eps, int center, void* out,
+                                  float* read_out, const int* row_index, int M, int out_dtype, cudaStream_t stream) {
+    SB_REQUIRE(M >= 0 && d > 0 && s >= 1 && s <= SMAX, "hyper_fold_norm: %d streams of %d (1 to %d streams)", s, d, SMAX);
+    SB_REQUIRE(SA >= 0 && SB >= 0 && (SA == 0 || a != nullptr) && (SB == 0 || b != nullptr),
+               "hyper_fold_norm: partial sums without a buffer");
+    SB_REQUIRE(SB == 0 || SA > 0, "hyper_fold_norm: a second branch without a first");
+    if (M == 0) return 0;
+    const size_t smem = (size_t)d * sizeof(float);
+    SB_REQUIRE(smem <= 200 * 1024, "hyper_fold_norm: width %d does not fit one block's shared memory", d);
+    HyperArgs h;
+    h.streams = streams; h.init = init; h.a = a; h.SA = SA; h.stride_a = (size_t)stride_a; h.scale_a = scale_a;
+    h.b = b; h.SB = SB; h.stride_b = (size_t)stride_b; h.scale_b = scale_b; h.bias = bias; h.mix = mix;
+    h.outw = outw; h.inw = inw; h.gain = gain; h.mult = mult; h.eps = eps; h.center = center; h.out = out;
+    h.read_out = read_out; h.row_index = row_index; h.s = s; h.d = d;
+    h.has_branch = SA > 0 || bias != nullptr;
+    h.write_streams = row_index == nullptr && (h.has_branch || init != nullptr);
+    int threads = ((d + 31) / 32) * 32;
+    if (threads > 256) threads = 256;
+    if (out_dtype == SB_F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(hyper_fold_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        sb::launch(hyper_fold_norm_kernel<float>, dim3(M), dim3(threads), smem, stream, h);
+    } else if (out_dtype == SB_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(hyper_fold_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        sb::launch(hyper_fold_norm_kernel<__nv_bfloat16>, dim3(M), dim3(threads), smem, stream, h);
+    } else {
+        SB_REQUIRE(false, "hyper_fold_norm: unknown dtype %d", out_dtype);
+    }
+    SB_LAUNCH_CHECK();
+}

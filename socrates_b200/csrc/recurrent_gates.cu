@@ -1,0 +1,235 @@
+// Two gated recurrences whose gates read only the current token, so that a prompt portion is one
+// walk over its tokens with the state in registers.
+//
+// min_gru: one state value per channel.
+//     z = sigmoid(pz + bz) ,  u = px + bx ,  c = u + 1/2 (u >= 0)  |  sigmoid(u) (u < 0)
+//     S <- (1 - z) S + z c ;  y = S * silu(pg)
+//   pz, px, pg are columns [0, W), [W, 2W), [2W, 3W) of one matrix product.
+//
+// gated_linear_attention: a matrix state per head in which the forget gate also decides what is written.
+//     q = silu(pq) ,  f = l + (1 - l) sigmoid(pf + bf)      (per head and key channel; l the lower bound)
+//     S <- diag(f) S + (1 - f) v^T ;  o = S^T q
+//     y = o / sqrt(mean(o^2) + eps) * w                     (per head, over its value dims)
+//
+// States are float32 and live in the request's state slot; gates, decays, the recurrences and the
+// norm are float32; only the products arrive in the model dtype and y leaves in it.
+#include <math.h>
+
+#include "common.cuh"
+
+using namespace sb;
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ------------------------------------------------------------------------------------ min_gru
+struct MinGruArgs {
+    const void* proj;          // [N, stride] in T
+    long long stride;
+    const float* bz;           // [W] or null
+    const float* bx;           // [W] or null
+    float* state;              // [rows, W]
+    void* out;                 // [N, W] in T
+    const int* seq_starts;
+    const int* seq_rows;
+    int W;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) min_gru_kernel(MinGruArgs a) {
+    sb::pdl_launch_dependents();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y, W = a.W;
+    const float bz = (c < W && a.bz) ? a.bz[c] : 0.f, bx = (c < W && a.bx) ? a.bx[c] : 0.f;
+    sb::pdl_wait();
+    if (c >= W) return;
+    const int t0 = a.seq_starts[r], t1 = a.seq_starts[r + 1];
+    if (t0 >= t1) return;
+    float* sp = a.state + (size_t)a.seq_rows[r] * W + c;
+    float S = *sp;
+    const T* p = (const T*)a.proj + c;
+    T* y = (T*)a.out + c;
+    constexpr int U = 8;               // tokens whose loads and gates are made before the chain runs over them
+    for (int tc = t0; tc < t1; tc += U) {
+        float z[U], cand[U], gate[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int t = min(tc + j, t1 - 1);
+            const T* row = p + (size_t)t * a.stride;
+            z[j] = to_float(row[0]);
+            cand[j] = to_float(row[W]);
+            gate[j] = to_float(row[2 * W]);
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            z[j] = sigmoidf_(z[j] + bz);
+            const float u = cand[j] + bx;
+            cand[j] = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+            gate[j] = gate[j] * sigmoidf_(gate[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            if (tc + j < t1) {
+                S = fmaf(z[j], cand[j] - S, S);            // (1 - z) S + z c
+                y[(size_t)(tc + j) * W] = from_float<T>(S * gate[j]);
+            }
+        }
+    }
+    *sp = S;
+}
+
+// ------------------------------------------------------------------------------------ gated linear attention
+struct GlaArgs {
+    const void* proj;          // [N, stride] in T: q at q_off (H*D), f at f_off (H*D), v at v_off (H*Dv)
+    long long stride;
+    int q_off, f_off, v_off;
+    const float* f_bias;       // [H*D] or null
+    const float* lower;        // [H*D] or null (0)
+    const float* norm_w;       // [Dv]
+    float* state;              // [rows, H, D, Dv]
+    void* out;                 // [N, H*Dv] in T
+    float* raw_o;              // [N, H*Dv]
+    const int* seq_starts;
+    const int* seq_rows;
+    int H, D, Dv;
+    float eps;
+};
+
+constexpr int RG = 16;         // threads that share a column of the state
+constexpr int COLS = 8;        // columns of a block
+constexpr int TB = 16;         // tokens staged at a time
+constexpr int GTHREADS = RG * COLS;
+
+template <typename T, int DR>
+__global__ void __launch_bounds__(GTHREADS) gla_kernel(GlaArgs a) {
+    sb::pdl_launch_dependents();
+    constexpr int DP = RG * DR;                       // padded key dims
+    __shared__ float fs[TB][DP + 4], qs[TB][DP + 4], vs[TB][COLS], os[TB][COLS];
+    const int h = blockIdx.x, r = blockIdx.y, c0 = blockIdx.z * COLS;
+    const int tid = threadIdx.x, rg = tid & (RG - 1), cj = tid / RG, j = c0 + cj;
+    const int D = a.D, Dv = a.Dv, H = a.H;
+    sb::pdl_wait();
+    const int t0 = a.seq_starts[r], t1 = a.seq_starts[r + 1];
+    if (t0 >= t1) return;
+    const T* proj = (const T*)a.proj;
+    const bool col = j < Dv;
+    float* sp = a.state + ((size_t)a.seq_rows[r] * H + h) * D * Dv + j;
+    float S[DR];
+#pragma unroll
+    for (int ii = 0; ii < DR; ++ii) {
+        const int i = rg + RG * ii;                   // thread rg owns rows rg, rg + 16, ...
+        S[ii] = (col && i < D) ? sp[(size_t)i * Dv] : 0.f;
+    }
+    for (int tc = t0; tc < t1; tc += TB) {
+        const int nt = min(TB, t1 - tc);
+        __syncthreads();
+        for (int i = tid; i < nt * DP; i += GTHREADS) {
+            const int tt = i / DP, d = i - tt * DP;
+            float f = 1.f, q = 0.f;                   // rows past D keep their zero state and read nothing
+            if (d < D) {
+                const T* row = proj + (size_t)(tc + tt) * a.stride;
+                const int ch = h * D + d;
+                const float l = a.lower ? a.lower[ch] : 0.f;
+                f = l + (1.0f - l) * sigmoidf_(to_float(row[a.f_off + ch]) + (a.f_bias ? a.f_bias[ch] : 0.f));
+                const float z = to_float(row[a.q_off + ch]);
+                q = z * sigmoidf_(z);
+            }
+            fs[tt][d] = f;
+            qs[tt][d] = q;
+        }
+        for (int i = tid; i < nt * COLS; i += GTHREADS) {
+            const int tt = i / COLS, c = i - tt * COLS;
+            vs[tt][c] = c0 + c < Dv ? to_float(proj[(size_t)(tc + tt) * a.stride + a.v_off + h * Dv + c0 + c]) : 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float v = vs[tt][cj];
+            float o = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < DR; ++ii) {
+                const float f = fs[tt][rg + RG * ii];
+                S[ii] = fmaf(f, S[ii] - v, v);        // f S + (1 - f) v
+                o = fmaf(S[ii], qs[tt][rg + RG * ii], o);
+            }
+#pragma unroll
+            for (int sh = 1; sh < RG; sh <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
+            if (rg == 0) os[tt][cj] = o;
+        }
+        __syncthreads();
+        for (int i = tid; i < nt * COLS; i += GTHREADS) {
+            const int tt = i / COLS, c = i - tt * COLS;
+            if (c0 + c < Dv) a.raw_o[(size_t)(tc + tt) * H * Dv + h * Dv + c0 + c] = os[tt][c];
+        }
+    }
+#pragma unroll
+    for (int ii = 0; ii < DR; ++ii) {
+        const int i = rg + RG * ii;
+        if (col && i < D) sp[(size_t)i * Dv] = S[ii];
+    }
+}
+
+// y = o / sqrt(mean(o^2) + eps) * w, a warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128) gla_out_kernel(GlaArgs a, int N) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= N * a.H) return;
+    const int Dv = a.Dv;
+    const float* o = a.raw_o + (size_t)item * Dv;
+    float ss = 0.f;
+    for (int j = lane; j < Dv; j += 32) ss += o[j] * o[j];
+    ss = warp_sum(ss);
+    const float rinv = 1.0f / sqrtf(ss / (float)Dv + a.eps);
+    T* y = (T*)a.out + (size_t)item * Dv;
+    for (int j = lane; j < Dv; j += 32) y[j] = from_float<T>(o[j] * rinv * a.norm_w[j]);
+}
+
+template <typename T>
+int launch_gla(const GlaArgs& a, int R, int N, cudaStream_t stream) {
+    const dim3 grid(a.H, R, (a.Dv + COLS - 1) / COLS);
+    if (a.D <= RG * 4) sb::launch(gla_kernel<T, 4>, grid, dim3(GTHREADS), 0, stream, a);
+    else if (a.D <= RG * 8) sb::launch(gla_kernel<T, 8>, grid, dim3(GTHREADS), 0, stream, a);
+    else sb::launch(gla_kernel<T, 16>, grid, dim3(GTHREADS), 0, stream, a);
+    sb::launch(gla_out_kernel<T>, dim3((N * a.H + 3) / 4), dim3(128), 0, stream, a, N);
+    SB_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+extern "C" int sb_min_gru(void* out, const void* proj, long long stride, const float* bz, const float* bx,
+                          float* state, const int* seq_starts, const int* seq_rows, int R, int W, int dtype,
+                          cudaStream_t stream) {
+    SB_REQUIRE(R >= 0 && W > 0 && stride >= 3LL * W, "min_gru: %d channels in rows of %lld", W, stride);
+    SB_REQUIRE(R <= 65535, "min_gru: %d requests exceed one launch", R);
+    if (R == 0) return 0;
+    MinGruArgs a;
+    a.proj = proj; a.stride = stride; a.bz = bz; a.bx = bx; a.state = state; a.out = out;
+    a.seq_starts = seq_starts; a.seq_rows = seq_rows; a.W = W;
+    const dim3 grid((W + 127) / 128, R);
+    if (dtype == SB_F32) sb::launch(min_gru_kernel<float>, grid, dim3(128), 0, stream, a);
+    else if (dtype == SB_BF16) sb::launch(min_gru_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, a);
+    else SB_REQUIRE(false, "min_gru: unknown dtype %d", dtype);
+    SB_LAUNCH_CHECK();
+}
+
+extern "C" int sb_gated_linear_attention_supports(int D, int Dv) { return D >= 1 && D <= 256 && Dv >= 1; }
+
+extern "C" int sb_gated_linear_attention(void* out, const void* proj, long long stride, int q_off, int f_off,
+                                         int v_off, const float* f_bias, const float* lower, const float* norm_w,
+                                         float* state, const int* seq_starts, const int* seq_rows, int R, int H,
+                                         int D, int Dv, float eps, int dtype, float* raw_o, int N,
+                                         cudaStream_t stream) {
+    SB_REQUIRE(R >= 0 && H > 0 && sb_gated_linear_attention_supports(D, Dv),
+               "gated_linear_attention: %d heads of %d (keys, at most 256) and %d (values) dims", H, D, Dv);
+    SB_REQUIRE(R <= 65535 && (Dv + COLS - 1) / COLS <= 65535, "gated_linear_attention: %d requests exceed one launch", R);
+    SB_REQUIRE(raw_o != nullptr && N >= 0, "gated_linear_attention: scratch for %d tokens is missing", N);
+    if (R == 0 || N == 0) return 0;
+    GlaArgs a;
+    a.proj = proj; a.stride = stride; a.q_off = q_off; a.f_off = f_off; a.v_off = v_off; a.f_bias = f_bias;
+    a.lower = lower; a.norm_w = norm_w; a.state = state; a.out = out; a.raw_o = raw_o;
+    a.seq_starts = seq_starts; a.seq_rows = seq_rows; a.H = H; a.D = D; a.Dv = Dv; a.eps = eps;
+    if (dtype == SB_F32) return launch_gla<float>(a, R, N, stream);
+    if (dtype == SB_BF16) return launch_gla<__nv_bfloat16>(a, R, N, stream);
+    SB_REQUIRE(false, "gated_linear_attention: unknown dtype %d", dtype);
+}

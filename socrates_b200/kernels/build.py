@@ -34,7 +34,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "sampling.cu", "gemm_simt.cu", "attention_simt.cu",
                 "gemm_tcgen05.cu", "gemm_tcgen05_rows.cu", "attention_mma.cu", "attention_decode.cu",
                 "attention_tcgen05.cu", "fold_norm.cu", "short_conv.cu", "retention.cu", "selective_scan.cu",
-                "attention_bias.cu", "delta_rule.cu", "moe_route.cu", "attention_diff.cu"]
+                "attention_bias.cu", "delta_rule.cu", "moe_route.cu", "attention_diff.cu", "hyper_norm.cu",
+                "recurrent_gates.cu", "gated_units.cu", "attention_talk.cu"]
 
 
 class BuildError(RuntimeError):

@@ -1060,3 +1060,253 @@ def diff_combine(out: torch.Tensor, maps: torch.Tensor, num_heads: int, lam: flo
     lib = library()
     check(lib, lib.sb_diff_combine(_ptr(out), _ptr(maps), N, num_heads, Dv, float(lam), float(eps), float(out_scale),
                                    _code(out.dtype), _stream()), "diff_combine")
+
+
+# Residual streams (hyper-connections), gated recurrences, attention with mixed scores, latent attention's
+# small steps.
+def hyper_fold_norm(streams: torch.Tensor, init: Optional[torch.Tensor], branch_a: Optional[torch.Tensor],
+                    scale_a: float, branch_b: Optional[torch.Tensor], scale_b: float, bias: Optional[torch.Tensor],
+                    mix: Optional[torch.Tensor], out_weights: Optional[torch.Tensor], mult: float,
+                    in_weights: Optional[torch.Tensor], gain: Optional[torch.Tensor], eps: float, center: bool,
+                    out: Optional[torch.Tensor], row_index: Optional[torch.Tensor] = None,
+                    read_out: Optional[torch.Tensor] = None) -> None:
+    """One pass over rows of `s` residual streams, streams float32 [N, s, d] (s = 1: [N, d], the ordinary
+    residual):
+        y   = scale_a * (sum(branch_a, 0) + bias) + scale_b * sum(branch_b, 0)     (what a sublayer left; optional)
+        x_t <- sum_f mix[f, t] x_f + mult * out_weights[t] * y                      (mix None: identity)
+        u   = sum_t in_weights[t] x_t                                               (None: the plain sum)
+        out = layer_norm(u) * gain (center) | rms_norm(u) * gain | u (gain None)
+    `init` float32 [N, d]: the streams do not exist yet and all start as init.  With `row_index` only those
+    rows are read and the streams stay as they are.  `read_out` float32 [M, d] receives u itself."""
+    _want(streams, "streams", torch.float32)
+    if streams.dim() == 2:
+        N, d = streams.shape
+        s = 1
+    elif streams.dim() == 3:
+        N, s, d = streams.shape
+    else:
+        raise KernelError(f"streams must be [N, s, d] or [N, d], got {tuple(streams.shape)}")
+    if init is not None:
+        _want(init, "init", torch.float32, (N, d))
+
+    def parts(t, name):
+        if t is None:
+            return 0
+        _want(t, name, torch.float32)
+        if t.dim() != 3 or t.shape[1:] != (N, d):
+            raise KernelError(f"{name} must be [S, {N}, {d}], got {tuple(t.shape)}")
+        return t.shape[0]
+
+    SA, SB = parts(branch_a, "branch_a"), parts(branch_b, "branch_b")
+    for t, name, shape in ((bias, "bias", (d,)), (mix, "mix", (s, s)), (out_weights, "out_weights", (s,)),
+                           (in_weights, "in_weights", (s,)), (gain, "gain", (d,))):
+        if t is not None:
+            _want(t, name, torch.float32, shape)
+    M = N
+    if row_index is not None:
+        _want(row_index, "row_index", torch.int32)
+        M = row_index.numel()
+    if out is not None:
+        _want(out, "out", None, (M, d))
+    if read_out is not None:
+        _want(read_out, "read_out", torch.float32, (M, d))
+    lib = library()
+    check(lib, lib.sb_hyper_fold_norm(_ptr(streams), _ptr(init), s, d, _ptr(branch_a), SA, N * d, float(scale_a),
+                                      _ptr(branch_b), SB, N * d, float(scale_b), _ptr(bias), _ptr(mix),
+                                      _ptr(out_weights), float(mult), _ptr(in_weights), _ptr(gain), float(eps),
+                                      int(bool(center)), _ptr(out), _ptr(read_out), _ptr(row_index), M,
+                                      _code(out.dtype) if out is not None else 0, _stream()), "hyper_fold_norm")
+
+
+def min_gru(out: torch.Tensor, proj: torch.Tensor, bias_z: Optional[torch.Tensor], bias_x: Optional[torch.Tensor],
+            state: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor) -> None:
+    """z = sigmoid(proj[:, :W] + bias_z); u = proj[:, W:2W] + bias_x; c = u + 1/2 where u >= 0, sigmoid(u) below;
+    S <- (1 - z) S + z c per channel, token after token of every request; out = S * silu(proj[:, 2W:3W]).
+    proj [N, >= 3W] in out's dtype; state float32 [rows, W] (the request's slot, carried on); out [N, W]."""
+    N, W = out.shape
+    _want(out, "out")
+    if proj.dim() != 2 or proj.shape[0] != N or proj.shape[1] < 3 * W or proj.stride(1) != 1 or proj.dtype != out.dtype:
+        raise KernelError(f"proj must be [{N}, >= {3 * W}] in {out.dtype} with unit column stride")
+    _want(state, "state", torch.float32)
+    if state.dim() != 2 or state.shape[1] != W:
+        raise KernelError(f"state must be [rows, {W}], got {tuple(state.shape)}")
+    for b, nm in ((bias_z, "bias_z"), (bias_x, "bias_x")):
+        if b is not None:
+            _want(b, nm, torch.float32, (W,))
+    R = seq_rows.numel()
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    lib = library()
+    check(lib, lib.sb_min_gru(_ptr(out), _ptr(proj), proj.stride(0), _ptr(bias_z), _ptr(bias_x), _ptr(state),
+                              _ptr(seq_starts), _ptr(seq_rows), R, W, _code(out.dtype), _stream()), "min_gru")
+
+
+def gated_linear_attention_supports(key_dim: int, value_dim: int) -> bool:
+    return bool(library().sb_gated_linear_attention_supports(key_dim, value_dim))
+
+
+def gated_linear_attention(out: torch.Tensor, proj: torch.Tensor, offsets: Tuple[int, int, int],
+                           f_bias: Optional[torch.Tensor], lower: Optional[torch.Tensor], norm_w: torch.Tensor,
+                           state: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor, num_heads: int,
+                           key_dim: int, value_dim: int, eps: float, scratch: torch.Tensor) -> None:
+    """Linear attention whose forget gate also decides what is written, token after token of every request:
+    q = silu(proj_q); f = lower + (1 - lower) * sigmoid(proj_f + f_bias); S <- diag(f) S + (1 - f) v^T; o = S^T q;
+    out = o / sqrt(mean(o^2) + eps) * norm_w per head.  `offsets` = columns where q (H*D), f (H*D) and v (H*Dv)
+    begin in proj; state float32 [rows, H, D, Dv]; scratch float32 [N, H*Dv] (the raw o)."""
+    H, D, Dv = num_heads, key_dim, value_dim
+    N = out.shape[0]
+    _want(out, "out", None, (N, H * Dv))
+    if proj.dim() != 2 or proj.shape[0] != N or proj.stride(1) != 1 or proj.dtype != out.dtype:
+        raise KernelError(f"proj must be [{N}, columns] in {out.dtype} with unit column stride")
+    q_off, f_off, v_off = offsets
+    if max(q_off + H * D, f_off + H * D, v_off + H * Dv) > proj.shape[1]:
+        raise KernelError("the column offsets reach past the rows of proj")
+    _want(state, "state", torch.float32)
+    if state.dim() != 4 or state.shape[1:] != (H, D, Dv):
+        raise KernelError(f"state must be [rows, {H}, {D}, {Dv}], got {tuple(state.shape)}")
+    for t, nm in ((f_bias, "f_bias"), (lower, "lower")):
+        if t is not None:
+            _want(t, nm, torch.float32, (H * D,))
+    _want(norm_w, "norm_w", torch.float32, (Dv,))
+    _want(scratch, "scratch", torch.float32)
+    if scratch.numel() < N * H * Dv:
+        raise KernelError("the scratch buffer is too small")
+    R = seq_rows.numel()
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    lib = library()
+    check(lib, lib.sb_gated_linear_attention(_ptr(out), _ptr(proj), proj.stride(0), q_off, f_off, v_off, _ptr(f_bias),
+                                             _ptr(lower), _ptr(norm_w), _ptr(state), _ptr(seq_starts), _ptr(seq_rows),
+                                             R, H, D, Dv, float(eps), _code(out.dtype), _ptr(scratch), N, _stream()),
+          "gated_linear_attention", kernels=2)
+
+
+def glu_clamp(out: torch.Tensor, x: torch.Tensor, bias_gate: Optional[torch.Tensor], bias_up: Optional[torch.Tensor],
+              limit: float, alpha: float, offset: float) -> None:
+    """g = min(x[:, :F] + bias_gate, limit); u = clamp(x[:, F:] + bias_up, -limit, limit);
+    out = g * sigmoid(alpha * g) * (u + offset).  x [N, 2F] in out's dtype or float32 partial sums [S, N, 2F]."""
+    N, F_ = out.shape
+    _want(out, "out")
+    parts = x.dim() == 3
+    if parts:
+        _want(x, "x partial sums", torch.float32, (x.shape[0], N, 2 * F_))
+    else:
+        _want(x, "x", out.dtype, (N, 2 * F_))
+    for b, nm in ((bias_gate, "bias_gate"), (bias_up, "bias_up")):
+        if b is not None:
+            _want(b, nm, torch.float32, (F_,))
+    lib = library()
+    check(lib, lib.sb_glu_clamp(_ptr(out), None if parts else _ptr(x), _ptr(x) if parts else None,
+                                x.shape[0] if parts else 0, N * 2 * F_, _ptr(bias_gate), _ptr(bias_up), N, F_,
+                                float(limit), float(alpha), float(offset), _code(out.dtype), _stream()), "glu_clamp")
+
+
+def scale_(x: torch.Tensor, c: float) -> None:
+    """x *= c in place; x float32."""
+    _want(x, "x", torch.float32)
+    lib = library()
+    check(lib, lib.sb_scale(_ptr(x), x.numel(), float(c), _stream()), "scale")
+
+
+def segment_norm(x: torch.Tensor, segments, eps: float) -> None:
+    """Runs of columns of x [N, columns], each RMS-normed over its own length with a gain (None: copied as it
+    is) and written to one or two places.  `segments`: up to four (begin, length, gain, [(tensor, column), ...])
+    with one or two destinations, matrices [N, >= column + length] of x's dtype with unit column stride."""
+    if x.dim() != 2 or x.stride(1) != 1 or not x.is_cuda:
+        raise KernelError("x must be a CUDA matrix with unit column stride")
+    N, n = x.shape[0], len(segments)
+    if not 1 <= n <= 4:
+        raise KernelError("segment_norm takes one to four segments")
+    IntArr, PtrArr, LLArr = ctypes.c_int * n, ctypes.c_void_p * n, ctypes.c_longlong * n
+    begin, length, gains = IntArr(), IntArr(), PtrArr()
+    d0, s0, o0, d1, s1, o1 = PtrArr(), LLArr(), IntArr(), PtrArr(), LLArr(), IntArr()
+    for i, (b, ln, gain, places) in enumerate(segments):
+        if b < 0 or ln < 1 or b + ln > x.shape[1]:
+            raise KernelError(f"segment {i} ({b}, {ln}) lies outside the {x.shape[1]} columns")
+        if gain is not None:
+            _want(gain, "gain", torch.float32, (ln,))
+        if not 1 <= len(places) <= 2:
+            raise KernelError("a segment goes to one or two places")
+        begin[i], length[i], gains[i] = b, ln, _ptr(gain)
+        for j, (t, col) in enumerate(places):
+            if (t.dim() != 2 or t.shape[0] != N or t.stride(1) != 1 or t.dtype != x.dtype or col < 0
+                    or col + ln > t.shape[1]):
+                raise KernelError(f"a destination must be [{N}, >= {col + ln}] in {x.dtype} with unit column stride")
+            if j == 0:
+                d0[i], s0[i], o0[i] = t.data_ptr(), t.stride(0), col
+            else:
+                d1[i], s1[i], o1[i] = t.data_ptr(), t.stride(0), col
+        if len(places) == 1:
+            d1[i], s1[i], o1[i] = None, 0, 0
+    lib = library()
+    check(lib, lib.sb_segment_norm(_ptr(x), x.stride(0), n, begin, length, gains, d0, s0, o0, d1, s1, o1, float(eps), N,
+                                   _code(x.dtype), _stream()), "segment_norm")
+
+
+def head_matmul(y: torch.Tensor, y_off: int, y_head: int, x: torch.Tensor, x_off: int, x_head: int, w: torch.Tensor,
+                num_heads: int, transposed: bool, carry: int = 0) -> None:
+    """A matrix per head: with W_h = rows h*A .. h*A + A - 1 of w [H*A, B],
+    y[n, y_off + h*y_head + :] = W_h x[n, x_off + h*x_head + :B]  (A outputs), or, `transposed`,
+    W_h^T x[n, x_off + h*x_head + :A]  (B outputs).  `carry`: the values in front of every head's input are
+    copied in front of its output.  Sums are float32; x, y, w share one dtype."""
+    H = num_heads
+    if w.dim() != 2 or w.shape[0] % H:
+        raise KernelError(f"w must be [{H} * A, B], got {tuple(w.shape)}")
+    A, B = w.shape[0] // H, w.shape[1]
+    _want(w, "w", x.dtype)
+    nin, nout = (A, B) if transposed else (B, A)
+    N = x.shape[0]
+    for t, nm, off, head, n in ((x, "x", x_off, x_head, nin), (y, "y", y_off, y_head, nout)):
+        if t.dim() != 2 or t.shape[0] != N or t.stride(1) != 1 or t.dtype != x.dtype or not t.is_cuda:
+            raise KernelError(f"{nm} must be a CUDA matrix [{N}, columns] in {x.dtype} with unit column stride")
+        if off + (H - 1) * head + n > t.shape[1] or off < carry:
+            raise KernelError(f"{nm}: {H} heads of {n} at {off} + h * {head} do not fit {t.shape[1]} columns")
+    lib = library()
+    check(lib, lib.sb_head_matmul(_ptr(y), y.stride(0), y_off, y_head, _ptr(x), x.stride(0), x_off, x_head, _ptr(w),
+                                  H, A, B, int(bool(transposed)), int(carry), N, _code(x.dtype), _stream()),
+          "head_matmul")
+
+
+def attention_talk_tile(num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int) -> int:
+    """Queries per tile the mixed-score attention kernel chooses for prompt portions; 0: it does not take the shape."""
+    return int(library().sb_attention_talk_tile(num_heads, num_kv_heads, key_dim, value_dim))
+
+
+def attention_talk(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                   block_table: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor,
+                   seq_first_pos: torch.Tensor, talk: torch.Tensor, num_heads: int, scale: float, window: int = 0,
+                   gate: Optional[torch.Tensor] = None, queries_per_tile: int = 0, num_partitions: int = 1,
+                   part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
+    """Paged causal attention whose scaled scores are mixed across heads before the softmax:
+    s_h = scale * sum_g talk[h, g] (q_g . k_kv(g)); o_h = softmax(s_h) v_kv(h) * sigmoid(gate_h) (gate [N, >= Hq*Dv],
+    optional).  Request r brings tokens seq_starts[r] .. seq_starts[r+1]-1 at positions seq_first_pos[r], +1, ...
+    of cache row seq_rows[r].  q [N, Hq*Dk], pools [pages, Hkv, BS, Dk | Dv], out [N, Hq*Dv].
+    `queries_per_tile` 0: chosen from the shape; 1 with `num_partitions` > 1 for decode steps: every token's keys
+    are cut into shares merged through float32 scratch part_o (N*Hq*NP*Dv) and part_ml (N*Hq*NP*2)."""
+    N = q.shape[0]
+    pages, Hkv, BS, Dk = k_pool.shape
+    Dv = v_pool.shape[3]
+    Hq = num_heads
+    R = seq_rows.numel()
+    _want(q, "q", k_pool.dtype, (N, Hq * Dk))
+    _want(out, "out", q.dtype, (N, Hq * Dv))
+    _want(k_pool, "k_pool")
+    _want(v_pool, "v_pool", k_pool.dtype, (pages, Hkv, BS, Dv))
+    _want(block_table, "block_table", torch.int32)
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    _want(seq_first_pos, "seq_first_pos", torch.int32, (R,))
+    _want(talk, "talk", torch.float32, (Hq, Hq))
+    gate_stride = _gate_stride(gate, q, N, Hq * Dv)
+    if num_partitions > 1:
+        _want(part_o, "part_o", torch.float32)
+        _want(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < N * Hq * num_partitions * Dv or part_ml.numel() < N * Hq * num_partitions * 2:
+            raise KernelError("attention scratch buffers are too small")
+    lib = library()
+    check(lib, lib.sb_attention_talk(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                     block_table.shape[1], _ptr(seq_starts), _ptr(seq_rows), _ptr(seq_first_pos), R,
+                                     _ptr(talk), _ptr(gate), gate_stride, N, Hq, Hkv, Dk, Dv, BS, int(window),
+                                     float(scale), int(queries_per_tile), int(num_partitions), _ptr(part_o),
+                                     _ptr(part_ml), _code(q.dtype), _stream()), "attention_talk",
+          kernels=2 if num_partitions > 1 else 1)

@@ -5,7 +5,8 @@ the built-in kinds."""
 from .base import (Branch, ParamSpec, Part, ResidualStream, build_part, register_part, registered,
                    unregister_part)
 from . import (norm, position, attention, feed_forward, block, embedding, stream_ops, retention,  # noqa: F401
-               window_attention, selective_scan, combine, sink_attention, delta_rule, routed_ff, diff_attention)                                       # (registration)
+               window_attention, selective_scan, combine, sink_attention, delta_rule, routed_ff, diff_attention, hyper,
+               gated_recurrence, talking_attention, latent_attention)                                       # (registration)
 from .linear import Linear
 
 __all__ = ["Branch", "ParamSpec", "Part", "ResidualStream", "build_part", "register_part",

@@ -88,15 +88,21 @@ class Branch:
     `bias` (float32 [d]) is added to their sum; with `post_gain` the sum is first normed
     (x / sqrt(mean(x^2) + post_eps) * post_gain) and joins the residual only then: a block
     that norms its branches on both sides sets these, and whoever folds the branch into the
-    residual (the next norm's kernel) does the arithmetic."""
+    residual (the next norm's kernel) does the arithmetic.
+
+    `scale` multiplies the sum (and its bias); `also` is a second branch that joins beside this
+    one with a scale of its own (two mixers side by side).  Only the folding kernel of the
+    residual streams (`parts/hyper.py`) takes these two."""
     partial: torch.Tensor
     bias: Optional[torch.Tensor] = None
     post_gain: Optional[torch.Tensor] = None
     post_eps: float = 0.0
+    scale: float = 1.0
+    also: Optional["Branch"] = None
 
     @property
     def plain(self) -> bool:
-        return self.bias is None and self.post_gain is None
+        return self.bias is None and self.post_gain is None and self.scale == 1.0 and self.also is None
 
 
 class ResidualStream:
@@ -109,6 +115,12 @@ class ResidualStream:
         self.add_rows: Optional[torch.Tensor] = None
         self.add_vec: Optional[torch.Tensor] = None
         self.embedding_output: Optional[torch.Tensor] = None   # kept by the model when a stream op asks
+        # Several residual streams (hyper-connections): float32 [N, s, d] once a block has made them
+        # (`fresh`: they are still to be filled from `residual`), and how the pending branch joins
+        # them: (mix [s, s], out weights [s], factor) left by the block that left the branch.
+        self.streams: Optional[torch.Tensor] = None
+        self.fresh = False
+        self.joining = None
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {

@@ -7,6 +7,11 @@ Each inner mixer is an ordinary registered mixer built from its own spec; its te
 under `<name><prefix_i>`, its gain is the tensor `<name><prefix_i>out`, and what it asks of
 the cache (pages, state slots) is passed through with the prefix in front of state names.
 The norms, the gains and the mean are one kernel that reads the inner products' partial sums.
+
+"scaled_sum": two mixers read the same input side by side and their outputs are added with a constant each:
+    out = scale_0 * mixer_0(x) + scale_1 * mixer_1(x)
+Nothing is computed here: the second branch rides with the first (`Branch.also`) and the kernel that folds
+the branch into the residual streams adds both, each with its scale.  Tensors and cache needs as above.
 """
 
 from __future__ import annotations
@@ -20,33 +25,30 @@ from ..kernels import ops
 from .base import Branch, ParamSpec, Part, build_part, register_part
 
 
-class NormedMean(Part):
+class _SideBySide(Part):
+    """Two inner mixers built from their own specs; tensors, graphs and cache needs passed through."""
     out_buffer = "branch"
 
     def __init__(self, spec, name):
         super().__init__(spec, name)
         p = spec.params
         self.hidden = int(p["hidden_size"])
-        self.eps = float(p["eps"])
         self.prefixes: List[str] = [str(s.name) for s in p["branches"]]
         self.inner = [build_part("mixer", s, name + s.name) for s in p["branches"]]
         if len(self.inner) != 2:
-            raise ValueError("the normed-mean kernel takes two branches")
+            raise ValueError("two branches run side by side")
         for i, m in enumerate(self.inner):
             m.out_buffer = f"branch.{i}"
-        self.gains = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
         out: Dict[str, ParamSpec] = {}
-        for pre, m in zip(self.prefixes, self.inner):
+        for m in self.inner:
             out.update(m.parameters())
-            out[self.name + pre + "out"] = ParamSpec((self.hidden,), role="gain", init="gain")
         return out
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
         for m in self.inner:
             m.bind(tensors, dtype)
-        self.gains = [tensors[self.name + pre + "out"] for pre in self.prefixes]
 
     @property
     def supports_graph(self) -> bool:
@@ -69,6 +71,24 @@ class NormedMean(Part):
     def streamed_weights(self):
         return [w for m in self.inner for w in getattr(m, "streamed_weights", list)()]
 
+
+class NormedMean(_SideBySide):
+    def __init__(self, spec, name):
+        super().__init__(spec, name)
+        self.eps = float(spec.params["eps"])
+        self.gains = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        out: Dict[str, ParamSpec] = {}
+        for pre, m in zip(self.prefixes, self.inner):
+            out.update(m.parameters())
+            out[self.name + pre + "out"] = ParamSpec((self.hidden,), role="gain", init="gain")
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
+        super().bind(tensors, dtype)
+        self.gains = [tensors[self.name + pre + "out"] for pre in self.prefixes]
+
     def forward(self, ctx, x: torch.Tensor, cache) -> Branch:
         N = x.shape[0]
         parts = [m.forward(ctx, x, cache.sub(pre)) for pre, m in zip(self.prefixes, self.inner)]
@@ -81,3 +101,25 @@ class NormedMean(Part):
 
 
 register_part("mixer", "normed_mean", NormedMean)
+
+
+class ScaledSum(_SideBySide):
+    def __init__(self, spec, name):
+        super().__init__(spec, name)
+        self.scales = [float(v) for v in spec.params["scales"]]
+        if len(self.scales) != 2:
+            raise ValueError("a scale for each of the two branches")
+
+    def forward(self, ctx, x: torch.Tensor, cache) -> Branch:
+        first, second = (m.forward(ctx, x, cache.sub(pre)) for pre, m in zip(self.prefixes, self.inner))
+        for b in (first, second):
+            if b.also is not None or b.post_gain is not None or b.scale != 1.0:
+                raise ValueError("an inner mixer's branch must be partial sums (and a bias, for the first)")
+        if second.bias is not None:
+            raise ValueError("only the first of two branches side by side may bring a bias")
+        first.scale, second.scale = self.scales
+        first.also = second
+        return first
+
+
+register_part("mixer", "scaled_sum", ScaledSum)

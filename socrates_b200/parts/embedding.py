@@ -3,7 +3,8 @@
 Embedding: x = table[ids] (model/qwen/qwen_kv_paged.py:198,219), widened to the
 float32 residual and multiplied by `scale` where the plan gives one.  Head: logits = x W^T with W the embedding table when the
 configuration ties them (:224) or `lm_head.weight` otherwise; only the rows whose
-logits were asked for are computed, in float32; with `softcap` c they become c * tanh(logits / c).
+logits were asked for are computed, in float32; with `softcap` c they become c * tanh(logits / c);
+with `scale` they are multiplied by a constant.
 """
 
 from __future__ import annotations
@@ -49,6 +50,7 @@ class LMHead(Part):
         self.softcap: Optional[float] = float(cap) if cap else None
         if self.softcap is not None and not self.softcap > 0:
             raise ValueError(f"a logit cap of {self.softcap}")
+        self.scale = float(spec.params.get("scale", 1.0))      # logits <- logits * scale, in float32
         self.linear: Optional[Linear] = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
@@ -68,6 +70,8 @@ class LMHead(Part):
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         logits = self.linear(ctx, x, "logits", out="wanted_float32")
+        if self.scale != 1.0:
+            ops.scale_(logits, self.scale)
         if self.softcap is not None:
             ops.softcap(logits, self.softcap)
         return logits

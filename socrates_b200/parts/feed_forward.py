@@ -105,3 +105,53 @@ class DenseFF(Part):
 
 
 register_part("feed_forward", "dense_act", DenseFF)
+
+
+class ClampedGLU(Part):
+    """A gated feed-forward whose gate and value are clamped, with biases on all three matrices:
+        g = min(W_gate x + b_gate, limit) ,  u = clamp(W_up x + b_up, -limit, limit)
+        out = W_down (g * sigmoid(alpha * g) * (u + offset)) + b_down
+    `limit`, `alpha` and `offset` come from the spec.  gate and up are one matrix product (gate rows first);
+    biases, clamps and the activation are one float32 kernel that reads the product (its split-K partial sums
+    where it was cut); the down bias travels with the branch.  Tensors: `<name>gate`, `gate.b`, `up`, `up.b`,
+    `down`, `down.b`."""
+
+    def __init__(self, spec, name):
+        super().__init__(spec, name)
+        p = spec.params
+        self.hidden, self.inter = int(p["hidden_size"]), int(p["intermediate_size"])
+        self.limit, self.alpha, self.offset = float(p["limit"]), float(p.get("alpha", 1.702)), float(p.get("offset", 1.0))
+        if not self.limit > 0:
+            raise ValueError(f"a clamp at {self.limit}")
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+        self.b_gate = self.b_up = self.b_down = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        n = self.name
+        return {
+            n + "gate": ParamSpec((self.inter, self.hidden)), n + "up": ParamSpec((self.inter, self.hidden)),
+            n + "down": ParamSpec((self.hidden, self.inter)),
+            n + "gate.b": ParamSpec((self.inter,), role="gain", init="around_zero"),
+            n + "up.b": ParamSpec((self.inter,), role="gain", init="around_zero"),
+            n + "down.b": ParamSpec((self.hidden,), role="gain", init="normal"),
+        }
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
+        n = self.name
+        self.gate_up = Linear(torch.cat([tensors[n + "gate"], tensors[n + "up"]], dim=0))
+        self.down = Linear(tensors[n + "down"])
+        self.b_gate, self.b_up, self.b_down = tensors[n + "gate.b"], tensors[n + "up.b"], tensors[n + "down.b"]
+
+    def streamed_weights(self):
+        return [self.gate_up.weight, self.down.weight]
+
+    def forward(self, ctx, x: torch.Tensor) -> Branch:
+        N = x.shape[0]
+        gu = self.gate_up(ctx, x, "gate_up", out="model_or_partial")
+        act = ctx.buffers.take("act", N, (self.inter,), ctx.dtype)
+        ops.glu_clamp(act, gu, self.b_gate, self.b_up, self.limit, self.alpha, self.offset)
+        return Branch(self.down(ctx, act, "branch", out="partial"), bias=self.b_down)
+
+
+register_part("feed_forward", "clamped_glu", ClampedGLU)

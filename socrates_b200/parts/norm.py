@@ -28,6 +28,9 @@ def fold_and_norm(stream: ResidualStream, gain: Optional[torch.Tensor], out: Opt
     (None: only the residual moves on).  With `row_index` only those rows are computed and nothing
     on the stream changes."""
     b = stream.pending
+    if stream.streams is not None or (b is not None and (b.scale != 1.0 or b.also is not None)):
+        raise ValueError("several residual streams, a scaled branch or two branches side by side are folded by "
+                         "the norms of parts/hyper.py; this norm takes the plain residual")
     plain = (b is None or b.plain) and stream.add_rows is None and stream.add_vec is None
     if plain and out is not None and gain is not None:
         ops.add_rmsnorm(stream.residual, b.partial if b is not None else None, gain, out, eps, row_index)
