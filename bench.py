@@ -5,6 +5,7 @@
     python bench.py --compare bofusun [--sizes 1k,2k,4k]     (another design beside Qwen3 at equal size)
     python bench.py --compare loletar [--sizes 1k,2k,4k]
     python bench.py --compare samerax [--sizes 1k,2k,4k]
+    python bench.py --compare magedra [--sizes 1k,2k,4k]
 
 Default run: the layer sizes of the Qwen3-4B shape (36 layers, hidden 2560, 32 query
 heads over 8 KV heads, head_dim 128, intermediate 9728, vocabulary 151936, tied head),
@@ -451,6 +452,27 @@ def _samerax(width, heads):
             "embedding": {"scale": 1.0}, "logit_softcap": 30.0, "layers": four + again}
 
 
+def _magedra(width, heads):
+    """A Magedra configuration at real layer widths, eight layer runs over four layers' weights: a minGRU of the
+    model's width; attention with mixed scores (heads of 128 dims, a quarter as many KV heads, half of the dims
+    rotating, gated) beside a gated linear attention of half as many heads with key rows of 64 and values of 128;
+    latent attention with heads of 128 + 64 dims over a latent of 128; a minGRU again; four residual streams;
+    clamped gated feed-forwards of four times the width."""
+    ff = {"kind": "dense", "ff": 4 * width, "limit": 7.0}
+    gru = {"type": "mingru", "mixer": {"width": width}, "mlp": dict(ff)}
+    par = {"type": "parallel", "mlp": dict(ff), "mixer": {
+        "left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "rot": {"dims": 64, "base": 1e6}},
+        "right": {"heads": max(1, heads // 2), "dim": 64, "vdim": 128}, "left_scale": 1.0, "right_scale": 1.0}}
+    lat = {"type": "latent_attention", "mlp": dict(ff), "mixer": {
+        "heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": width // 2, "kv_rank": 128,
+        "scale": 192 ** -0.5, "rot": {"base": 1e4, "dims": 64}}}
+    four = [gru, par, lat, dict(gru, mixer=dict(gru["mixer"]))]
+    again = [dict(l, weights_of=i) for i, l in enumerate(four)]
+    return {"architecture": "Magedra", "vocab": 32000, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "streams": 4, "logit_scale": 1.0, "layers": four + again}
+
+
 def _qwen3_like(width, runs, heads):
     """The Qwen3 decoder at the same width, number of layer runs, head size and feed-forward width."""
     return {"architectures": ["Qwen3ForCausalLM"], "vocab_size": 32000, "hidden_size": width,
@@ -460,7 +482,7 @@ def _qwen3_like(width, runs, heads):
 
 
 def run_compare(args):
-    """`--compare bofusun|loletar|samerax`: prefill and decode throughput of another design at real layer widths
+    """`--compare bofusun|loletar|samerax|magedra`: prefill and decode throughput of another design at real layer widths
     (random weights) beside the Qwen3 decoder at equal width, layer runs and head size.  One JSON line."""
     import torch
 
@@ -483,7 +505,7 @@ def run_compare(args):
         width, heads = sizes[size]
         design = args.compare
         bof = {"bofusun": lambda: _bofusun(width, 5, heads, 1024), "loletar": lambda: _loletar(width, heads),
-               "samerax": lambda: _samerax(width, heads)}[design]()
+               "samerax": lambda: _samerax(width, heads), "magedra": lambda: _magedra(width, heads)}[design]()
         runs = len(config_from_dict(bof).plan().order)
         only = [x for x in (args.only.split(",") if args.only else [design, "qwen3"])]
         for label, cfg_dict in ((design, bof), ("qwen3", _qwen3_like(width, runs, heads))):
@@ -607,8 +629,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
-    ap.add_argument("--compare", default=None, choices=("bofusun", "loletar", "samerax"),
-                    help="the Bofusun, the Loletar or the Samerax design at real layer widths beside Qwen3 at equal size "
+    ap.add_argument("--compare", default=None, choices=("bofusun", "loletar", "samerax", "magedra"),
+                    help="the Bofusun, the Loletar, the Samerax or the Magedra design at real layer widths beside Qwen3 at equal size "
                          "(prefill and decode); the default workload is not run")
     ap.add_argument("--only", default=None, help="with --compare: run only these of the pair, e.g. 'loletar' or 'qwen3'")
     ap.add_argument("--sizes", default=None, help="with --compare: widths to run, of 1k,2k,4k (default 1k,2k)")

@@ -24,7 +24,7 @@ namespace {
 constexpr int THREADS = 128;
 constexpr int KEYS = 128;      // keys per chunk: one per thread
 constexpr int HEADS = 4;       // query heads per pass over the keys
-constexpr int DMAX = 256;
+constexpr int DMAX = 576;
 
 struct BiasAttnArgs {
     void* out;                 // [N, Hq*Dv] in T
@@ -410,7 +410,7 @@ extern "C" int sb_attention_bias(void* out, const void* q, const void* k_pool, c
 // Returns SB_ERR_ARG for shapes the tile kernel does not take; `sb_attention_bias_tile_supports` says which.
 extern "C" int sb_attention_bias_tile_supports(int Hq, int Hkv, int Dk, int Dv, int dtype) {
     const int vec = dtype == SB_BF16 ? 8 : 4;
-    return Hq % Hkv == 0 && Dk % vec == 0 && Dk >= vec && Dk <= 256 && Dv >= 1 && Dv <= THREADS;
+    return Hq % Hkv == 0 && Dk % vec == 0 && Dk >= vec && Dk <= DMAX && Dv >= 1 && Dv <= THREADS;
 }
 
 extern "C" int sb_attention_bias_tile(void* out, const void* q, const void* k_pool, const void* v_pool,

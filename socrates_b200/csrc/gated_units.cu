@@ -7,6 +7,9 @@
 //                  (or y = x without a gain), written to one or two places
 //   head_matmul:   y[n, h, :] = W_h x[n, h, :]  or  W_h^T x[n, h, :],  W_h = rows h*A .. h*A + A - 1 of W [H*A, B]
 //   scale:         x *= c
+//   latent_write:  per token: c = rmsnorm(latent) * w; the shared key part and every query head's first `dr`
+//                  dims are turned by the token's position; the row [turned key part | c] goes into the key
+//                  page and c into the value page (one head), the queries are turned in place
 #include <math.h>
 
 #include "common.cuh"
@@ -154,6 +157,71 @@ __global__ void __launch_bounds__(128) head_matmul_kernel(HeadArgs a) {
     }
 }
 
+struct LatentArgs {
+    const void* down;          // [N, stride] in T: the latent at c_off (rank), the shared key part at r_off (dr)
+    long long stride;
+    int c_off, r_off, rank, dr;
+    const float* gain;         // [rank]
+    float eps;
+    void* q;                   // [N, H*D] in T, D = dr + rank: every head's first dr dims are turned in place
+    int H;
+    const float* inv_freq;     // [dr / 2]
+    int neighbours;            // 1: dim 2j turns with 2j + 1; 0: dim j with j + dr/2
+    float magnitude;
+    const int* positions;
+    const int* token_rows;
+    const int* block_table;
+    int table_width, BS;
+    void* k_pool;              // [pages, 1, BS, D]
+    void* v_pool;              // [pages, 1, BS, rank]
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) latent_write_kernel(LatentArgs a) {
+    sb::pdl_launch_dependents();
+    extern __shared__ float cs[];           // dr/2 cosines, then dr/2 sines
+    __shared__ float scratch[33];
+    const int n = blockIdx.x, half = a.dr / 2, D = a.dr + a.rank;
+    sb::pdl_wait();
+    const int pos = a.positions[n];
+    const int page = a.block_table[(size_t)a.token_rows[n] * a.table_width + pos / a.BS];
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float ang = (float)pos * a.inv_freq[j];
+        cs[j] = cosf(ang) * a.magnitude;
+        cs[half + j] = sinf(ang) * a.magnitude;
+    }
+    const T* row = (const T*)a.down + (size_t)n * a.stride;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < a.rank; i += blockDim.x) {
+        const float v = to_float(row[a.c_off + i]);
+        ss += v * v;
+    }
+    const float rinv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)a.rank + a.eps);      // (its barriers also publish cs)
+    const size_t slot = (size_t)page * a.BS + pos % a.BS;
+    T* kr = (T*)a.k_pool + slot * D;
+    T* vr = (T*)a.v_pool + slot * a.rank;
+    for (int i = threadIdx.x; i < a.rank; i += blockDim.x) {
+        const T c = from_float<T>(to_float(row[a.c_off + i]) * rinv * a.gain[i]);
+        kr[a.dr + i] = c;
+        vr[i] = c;
+    }
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const int ia = a.neighbours ? 2 * j : j, ib = a.neighbours ? 2 * j + 1 : j + half;
+        const float u = to_float(row[a.r_off + ia]), v = to_float(row[a.r_off + ib]);
+        kr[ia] = from_float<T>(u * cs[j] - v * cs[half + j]);
+        kr[ib] = from_float<T>(v * cs[j] + u * cs[half + j]);
+    }
+    T* q = (T*)a.q + (size_t)n * a.H * D;
+    for (int i = threadIdx.x; i < a.H * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        const int ia = a.neighbours ? 2 * j : j, ib = a.neighbours ? 2 * j + 1 : j + half;
+        T* qh = q + (size_t)h * D;
+        const float u = to_float(qh[ia]), v = to_float(qh[ib]);
+        qh[ia] = from_float<T>(u * cs[j] - v * cs[half + j]);
+        qh[ib] = from_float<T>(v * cs[j] + u * cs[half + j]);
+    }
+}
+
 inline int blocks_for(size_t total) { return (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8); }
 
 }  // namespace
@@ -220,5 +288,26 @@ extern "C" int sb_head_matmul(void* y, long long y_stride, int y_off, int y_head
     if (dtype == SB_F32) sb::launch(head_matmul_kernel<float>, grid, dim3(128), 0, stream, a);
     else if (dtype == SB_BF16) sb::launch(head_matmul_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, a);
     else SB_REQUIRE(false, "head_matmul: unknown dtype %d", dtype);
+    SB_LAUNCH_CHECK();
+}
+
+extern "C" int sb_latent_write(const void* down, long long stride, int c_off, int r_off, int rank, int dr,
+                               const float* gain, float eps, void* q, int H, const float* inv_freq, int neighbours,
+                               float magnitude, const int* positions, const int* token_rows, const int* block_table,
+                               int table_width, int page_size, void* k_pool, void* v_pool, int N, int dtype,
+                               cudaStream_t stream) {
+    SB_REQUIRE(N >= 0 && H > 0 && rank > 0 && dr >= 0 && dr % 2 == 0, "latent_write: bad sizes H=%d rank=%d dr=%d", H, rank, dr);
+    SB_REQUIRE(page_size > 0 && table_width > 0, "latent_write: bad page_size %d or table width %d", page_size, table_width);
+    SB_REQUIRE(dr == 0 || inv_freq != nullptr, "latent_write: turning dims without a frequency table");
+    if (N == 0) return 0;
+    LatentArgs a;
+    a.down = down; a.stride = stride; a.c_off = c_off; a.r_off = r_off; a.rank = rank; a.dr = dr; a.gain = gain;
+    a.eps = eps; a.q = q; a.H = H; a.inv_freq = inv_freq; a.neighbours = neighbours; a.magnitude = magnitude;
+    a.positions = positions; a.token_rows = token_rows; a.block_table = block_table; a.table_width = table_width;
+    a.BS = page_size; a.k_pool = k_pool; a.v_pool = v_pool;
+    const size_t smem = (size_t)(dr > 0 ? dr : 2) * sizeof(float);
+    if (dtype == SB_F32) sb::launch(latent_write_kernel<float>, dim3(N), dim3(128), smem, stream, a);
+    else if (dtype == SB_BF16) sb::launch(latent_write_kernel<__nv_bfloat16>, dim3(N), dim3(128), smem, stream, a);
+    else SB_REQUIRE(false, "latent_write: unknown dtype %d", dtype);
     SB_LAUNCH_CHECK();
 }

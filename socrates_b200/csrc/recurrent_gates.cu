@@ -36,46 +36,72 @@ struct MinGruArgs {
     int W;
 };
 
+// The recurrence S <- a S + b (a = 1 - z, b = z c) is linear in S, so a request's tokens are cut into
+// `segs` segments that run side by side: every thread (a channel, a segment) first walks its segment from a
+// zero state and keeps the product of its a's; the segments' results are joined in order through shared memory
+// (the state at a segment's start = what the earlier segments leave); then it walks its segment again from its
+// true start state and writes the outputs.  One segment (a decode step): a single walk.
 template <typename T>
-__global__ void __launch_bounds__(128) min_gru_kernel(MinGruArgs a) {
+__device__ __forceinline__ void gru_inputs(const T* row, int W, float bz, float bx, float& z, float& c, float& gate) {
+    z = sigmoidf_(to_float(row[0]) + bz);
+    const float u = to_float(row[W]) + bx;
+    c = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+    const float gz = to_float(row[2 * W]);
+    gate = gz * sigmoidf_(gz);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024) min_gru_kernel(MinGruArgs a, int segs) {
     sb::pdl_launch_dependents();
-    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y, W = a.W;
-    const float bz = (c < W && a.bz) ? a.bz[c] : 0.f, bx = (c < W && a.bx) ? a.bx[c] : 0.f;
+    extern __shared__ float carry[];            // [segs][32] products of a, then [segs][32] states from zero
+    const int lane = threadIdx.x, sg = threadIdx.y;
+    const int c = blockIdx.x * 32 + lane, r = blockIdx.y, W = a.W;
+    const bool live = c < W;
+    const float bz = (live && a.bz) ? a.bz[c] : 0.f, bx = (live && a.bx) ? a.bx[c] : 0.f;
     sb::pdl_wait();
-    if (c >= W) return;
     const int t0 = a.seq_starts[r], t1 = a.seq_starts[r + 1];
     if (t0 >= t1) return;
+    const int per = (t1 - t0 + segs - 1) / segs;
+    const int lo = min(t1, t0 + sg * per), hi = min(t1, lo + per);
     float* sp = a.state + (size_t)a.seq_rows[r] * W + c;
-    float S = *sp;
     const T* p = (const T*)a.proj + c;
     T* y = (T*)a.out + c;
-    constexpr int U = 8;               // tokens whose loads and gates are made before the chain runs over them
-    for (int tc = t0; tc < t1; tc += U) {
+    constexpr int U = 4;                        // tokens whose loads and gates are made before the chain runs over them
+    float S = (segs == 1 && live) ? *sp : 0.f;
+    if (segs > 1) {
+        float A = 1.f;
+        if (live) {
+            for (int tc = lo; tc < hi; tc += U) {
+                float z[U], cand[U], gate[U];
+#pragma unroll
+                for (int j = 0; j < U; ++j) gru_inputs(p + (size_t)min(tc + j, hi - 1) * a.stride, W, bz, bx, z[j], cand[j], gate[j]);
+#pragma unroll
+                for (int j = 0; j < U; ++j)
+                    if (tc + j < hi) { S = fmaf(z[j], cand[j] - S, S); A *= 1.f - z[j]; }
+            }
+        }
+        carry[sg * 32 + lane] = A;
+        carry[(segs + sg) * 32 + lane] = S;
+        __syncthreads();
+        S = live ? *sp : 0.f;                   // the request's state, carried through the segments before this one
+        for (int k = 0; k < sg; ++k) S = fmaf(carry[k * 32 + lane], S, carry[(segs + k) * 32 + lane]);
+        if (sg == segs - 1 && live)             // the last segment also knows the state the request leaves
+            *sp = fmaf(carry[sg * 32 + lane], S, carry[(segs + sg) * 32 + lane]);
+    }
+    if (!live) return;
+    for (int tc = lo; tc < hi; tc += U) {
         float z[U], cand[U], gate[U];
 #pragma unroll
-        for (int j = 0; j < U; ++j) {
-            const int t = min(tc + j, t1 - 1);
-            const T* row = p + (size_t)t * a.stride;
-            z[j] = to_float(row[0]);
-            cand[j] = to_float(row[W]);
-            gate[j] = to_float(row[2 * W]);
-        }
+        for (int j = 0; j < U; ++j) gru_inputs(p + (size_t)min(tc + j, hi - 1) * a.stride, W, bz, bx, z[j], cand[j], gate[j]);
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            z[j] = sigmoidf_(z[j] + bz);
-            const float u = cand[j] + bx;
-            cand[j] = u >= 0.f ? u + 0.5f : sigmoidf_(u);
-            gate[j] = gate[j] * sigmoidf_(gate[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < U; ++j) {
-            if (tc + j < t1) {
+            if (tc + j < hi) {
                 S = fmaf(z[j], cand[j] - S, S);            // (1 - z) S + z c
                 y[(size_t)(tc + j) * W] = from_float<T>(S * gate[j]);
             }
         }
     }
-    *sp = S;
+    if (segs == 1) *sp = S;
 }
 
 // ------------------------------------------------------------------------------------ gated linear attention
@@ -197,18 +223,22 @@ int launch_gla(const GlaArgs& a, int R, int N, cudaStream_t stream) {
 
 }  // namespace
 
+// `longest`: an upper bound of the tokens any request brings (the launch shape depends on it, not the result).
 extern "C" int sb_min_gru(void* out, const void* proj, long long stride, const float* bz, const float* bx,
-                          float* state, const int* seq_starts, const int* seq_rows, int R, int W, int dtype,
-                          cudaStream_t stream) {
+                          float* state, const int* seq_starts, const int* seq_rows, int R, int W, int longest,
+                          int dtype, cudaStream_t stream) {
     SB_REQUIRE(R >= 0 && W > 0 && stride >= 3LL * W, "min_gru: %d channels in rows of %lld", W, stride);
     SB_REQUIRE(R <= 65535, "min_gru: %d requests exceed one launch", R);
     if (R == 0) return 0;
     MinGruArgs a;
     a.proj = proj; a.stride = stride; a.bz = bz; a.bx = bx; a.state = state; a.out = out;
     a.seq_starts = seq_starts; a.seq_rows = seq_rows; a.W = W;
-    const dim3 grid((W + 127) / 128, R);
-    if (dtype == SB_F32) sb::launch(min_gru_kernel<float>, grid, dim3(128), 0, stream, a);
-    else if (dtype == SB_BF16) sb::launch(min_gru_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, a);
+    int segs = (longest + 15) / 16;             // at least 16 tokens a segment, at most 32 segments
+    segs = segs < 1 ? 1 : (segs > 32 ? 32 : segs);
+    const dim3 grid((W + 31) / 32, R), block(32, segs);
+    const size_t smem = (size_t)2 * segs * 32 * sizeof(float);
+    if (dtype == SB_F32) sb::launch(min_gru_kernel<float>, grid, block, smem, stream, a, segs);
+    else if (dtype == SB_BF16) sb::launch(min_gru_kernel<__nv_bfloat16>, grid, block, smem, stream, a, segs);
     else SB_REQUIRE(false, "min_gru: unknown dtype %d", dtype);
     SB_LAUNCH_CHECK();
 }

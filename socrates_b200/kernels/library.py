@@ -71,13 +71,14 @@ _SIGNATURES = {
     "sb_attention_diff_tile_supports": [I, I, I, I, I],
     "sb_attention_diff_tile": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, F, I, P],
     "sb_hyper_fold_norm": [P, P, I, I, P, I, LL, F, P, I, LL, F, P, P, P, F, P, P, F, I, P, P, P, I, I, P],
-    "sb_min_gru": [P, P, LL, P, P, P, P, P, I, I, I, P],
+    "sb_min_gru": [P, P, LL, P, P, P, P, P, I, I, I, I, P],
     "sb_gated_linear_attention_supports": [I, I],
     "sb_gated_linear_attention": [P, P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, F, I, P, I, P],
     "sb_glu_clamp": [P, P, P, I, LL, P, P, I, I, F, F, F, I, P],
     "sb_scale": [P, LL, F, P],
     "sb_segment_norm": [P, LL, I, P, P, P, P, P, P, P, P, P, F, I, I, P],
     "sb_head_matmul": [P, LL, I, I, P, LL, I, I, P, I, I, I, I, I, I, I, P],
+    "sb_latent_write": [P, LL, I, I, I, I, P, F, P, I, P, I, F, P, P, P, I, I, P, P, I, I, P],
     "sb_attention_talk_tile": [I, I, I, I],
     "sb_attention_talk": [P, P, P, P, P, I, P, P, P, I, P, P, LL, I, I, I, I, I, I, I, F, I, I, P, P, I, P],
     "sb_attention_bias": [P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P, P, I, I, I, F, P],

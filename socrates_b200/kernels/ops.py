@@ -1119,10 +1119,12 @@ def hyper_fold_norm(streams: torch.Tensor, init: Optional[torch.Tensor], branch_
 
 
 def min_gru(out: torch.Tensor, proj: torch.Tensor, bias_z: Optional[torch.Tensor], bias_x: Optional[torch.Tensor],
-            state: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor) -> None:
+            state: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor, longest: Optional[int] = None) -> None:
     """z = sigmoid(proj[:, :W] + bias_z); u = proj[:, W:2W] + bias_x; c = u + 1/2 where u >= 0, sigmoid(u) below;
     S <- (1 - z) S + z c per channel, token after token of every request; out = S * silu(proj[:, 2W:3W]).
-    proj [N, >= 3W] in out's dtype; state float32 [rows, W] (the request's slot, carried on); out [N, W]."""
+    proj [N, >= 3W] in out's dtype; state float32 [rows, W] (the request's slot, carried on); out [N, W].
+    `longest`: an upper bound of the tokens one request brings (default N - R + 1); long portions are cut into
+    segments that run side by side and are joined in order."""
     N, W = out.shape
     _want(out, "out")
     if proj.dim() != 2 or proj.shape[0] != N or proj.shape[1] < 3 * W or proj.stride(1) != 1 or proj.dtype != out.dtype:
@@ -1138,7 +1140,8 @@ def min_gru(out: torch.Tensor, proj: torch.Tensor, bias_z: Optional[torch.Tensor
     _want(seq_rows, "seq_rows", torch.int32, (R,))
     lib = library()
     check(lib, lib.sb_min_gru(_ptr(out), _ptr(proj), proj.stride(0), _ptr(bias_z), _ptr(bias_x), _ptr(state),
-                              _ptr(seq_starts), _ptr(seq_rows), R, W, _code(out.dtype), _stream()), "min_gru")
+                              _ptr(seq_starts), _ptr(seq_rows), R, W, int(longest if longest is not None else N - R + 1),
+                              _code(out.dtype), _stream()), "min_gru")
 
 
 def gated_linear_attention_supports(key_dim: int, value_dim: int) -> bool:
@@ -1265,6 +1268,39 @@ def head_matmul(y: torch.Tensor, y_off: int, y_head: int, x: torch.Tensor, x_off
     check(lib, lib.sb_head_matmul(_ptr(y), y.stride(0), y_off, y_head, _ptr(x), x.stride(0), x_off, x_head, _ptr(w),
                                   H, A, B, int(bool(transposed)), int(carry), N, _code(x.dtype), _stream()),
           "head_matmul")
+
+
+def latent_write(down: torch.Tensor, c_off: int, r_off: int, rank: int, rot_dim: int, gain: torch.Tensor, eps: float,
+                 q: torch.Tensor, num_heads: int, inv_freq: torch.Tensor, neighbours: bool, magnitude: float,
+                 positions: torch.Tensor, token_rows: torch.Tensor, block_table: torch.Tensor, k_pool: torch.Tensor,
+                 v_pool: torch.Tensor) -> None:
+    """Per token: c = rmsnorm(down[:, c_off : c_off + rank]) * gain; the key part down[:, r_off : r_off + rot_dim]
+    and the first rot_dim dims of every head of q [N, H * (rot_dim + rank)] are turned by the token's position
+    (q in place); the row [turned key part | c] is written to the token's slot of k_pool [pages, 1, BS, rot_dim +
+    rank] and c to v_pool [pages, 1, BS, rank].  Norm and angles are float32."""
+    N, D = q.shape[0], rot_dim + rank
+    _want(q, "q", None, (N, num_heads * D))
+    if down.dim() != 2 or down.shape[0] != N or down.stride(1) != 1 or down.dtype != q.dtype or not down.is_cuda:
+        raise KernelError(f"down must be a CUDA matrix [{N}, columns] in {q.dtype} with unit column stride")
+    if max(c_off + rank, r_off + rot_dim) > down.shape[1]:
+        raise KernelError("the column offsets reach past the rows of down")
+    _want(gain, "gain", torch.float32, (rank,))
+    _want(inv_freq, "inv_freq", torch.float32)
+    if inv_freq.numel() < rot_dim // 2:
+        raise KernelError(f"inv_freq has {inv_freq.numel()} entries for {rot_dim} turning dims")
+    _want(positions, "positions", torch.int32, (N,))
+    _want(token_rows, "token_rows", torch.int32, (N,))
+    _want(block_table, "block_table", torch.int32)
+    _want(k_pool, "k_pool", q.dtype)
+    if k_pool.dim() != 4 or k_pool.shape[1] != 1 or k_pool.shape[3] != D:
+        raise KernelError(f"k_pool must be [pages, 1, page_size, {D}], got {tuple(k_pool.shape)}")
+    _want(v_pool, "v_pool", q.dtype, (*k_pool.shape[:3], rank))
+    lib = library()
+    check(lib, lib.sb_latent_write(_ptr(down), down.stride(0), c_off, r_off, rank, rot_dim, _ptr(gain), float(eps),
+                                   _ptr(q), num_heads, _ptr(inv_freq), int(bool(neighbours)), float(magnitude),
+                                   _ptr(positions), _ptr(token_rows), _ptr(block_table), block_table.shape[1],
+                                   k_pool.shape[2], _ptr(k_pool), _ptr(v_pool), N, _code(q.dtype), _stream()),
+          "latent_write")
 
 
 def attention_talk_tile(num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int) -> int:

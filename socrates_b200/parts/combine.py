@@ -104,14 +104,39 @@ register_part("mixer", "normed_mean", NormedMean)
 
 
 class ScaledSum(_SideBySide):
+    """Inner mixers that can take their projections from outside (`shared_projection = True`: their input
+    projections are one `Linear` named `proj`, and `forward` accepts `proj=(matrix, first column)`) share ONE
+    matrix product: the two weight matrices are laid one under the other when the weights are bound."""
+
     def __init__(self, spec, name):
         super().__init__(spec, name)
         self.scales = [float(v) for v in spec.params["scales"]]
         if len(self.scales) != 2:
             raise ValueError("a scale for each of the two branches")
+        self.fused = None
+        self.columns = [0, 0]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
+        super().bind(tensors, dtype)
+        if all(getattr(m, "shared_projection", False) for m in self.inner):
+            from .linear import Linear
+            self.columns = [0, self.inner[0].proj.out_features]
+            self.fused = Linear(torch.cat([m.proj.weight for m in self.inner], dim=0))
+            for m in self.inner:
+                m.proj = None                    # the rows live in the shared matrix now
+
+    def streamed_weights(self):
+        if self.fused is None:
+            return super().streamed_weights()
+        return [self.fused.weight, *[m.o.weight for m in self.inner]]
 
     def forward(self, ctx, x: torch.Tensor, cache) -> Branch:
-        first, second = (m.forward(ctx, x, cache.sub(pre)) for pre, m in zip(self.prefixes, self.inner))
+        if self.fused is not None:
+            proj = self.fused(ctx, x, "side_proj")
+            first, second = (m.forward(ctx, x, cache.sub(pre), proj=(proj, col))
+                             for pre, m, col in zip(self.prefixes, self.inner, self.columns))
+        else:
+            first, second = (m.forward(ctx, x, cache.sub(pre)) for pre, m in zip(self.prefixes, self.inner))
         for b in (first, second):
             if b.also is not None or b.post_gain is not None or b.scale != 1.0:
                 raise ValueError("an inner mixer's branch must be partial sums (and a bias, for the first)")

@@ -77,6 +77,7 @@ register_part("mixer", "min_gru", MinGRU)
 
 class GatedLinearAttention(Part):
     out_buffer = "branch"
+    shared_projection = True       # a mixer that holds this one may make the projections
 
     def __init__(self, spec, name):
         super().__init__(spec, name)
@@ -111,14 +112,14 @@ class GatedLinearAttention(Part):
         return CacheNeeds(state={"S": StateSpec((self.H, self.dk, self.dv), torch.float32)})
 
     def streamed_weights(self):
-        return [self.proj.weight, self.o.weight]
+        return [*([self.proj.weight] if self.proj is not None else []), self.o.weight]
 
-    def forward(self, ctx, x: torch.Tensor, cache) -> Branch:
+    def forward(self, ctx, x: torch.Tensor, cache, proj=None) -> Branch:
         N = x.shape[0]
-        proj = self.proj(ctx, x, "gla_proj")
+        proj, c0 = (self.proj(ctx, x, "gla_proj"), 0) if proj is None else proj      # or columns of a wider product
         y = ctx.buffers.take("gla_y", N, (self.Cv,), ctx.dtype)
         raw = ctx.buffers.take("gla_raw", N, (self.Cv,), torch.float32)
-        ops.gated_linear_attention(y, proj, (0, self.Cqk, 2 * self.Cqk), self.f_bias, self.lower, self.norm_w,
+        ops.gated_linear_attention(y, proj, (c0, c0 + self.Cqk, c0 + 2 * self.Cqk), self.f_bias, self.lower, self.norm_w,
                                    cache.state("S"), ctx.seq_starts, ctx.seq_rows, self.H, self.dk, self.dv,
                                    self.eps, scratch=raw)
         return Branch(self.o(ctx, y, self.out_buffer, out="partial"))

@@ -11,7 +11,8 @@ Keys and values are never made: q_h . (W_uk,h c) = (W_uk,h^T q_h) . c, so the qu
 latent space (a matrix per head), the cache holds the row [k_rot | c] as the ONE key head of `rot_dim +
 kv_rank` dims with c again as its value, the engine's paged attention runs `heads` query heads over that one
 head, and its output (sum_j p c_j per head) goes through W_uv,h afterwards.  The rows of W_uq are reordered
-when the weights are bound so that every head's turning part comes first, where the rotation kernel turns.
+when the weights are bound so that every head's turning part comes first.  One kernel norms the latent, turns
+the key part and the queries and writes the token's row into its pages.
 Norms, angles, scores, weights and sums are float32; the per-head matrices accumulate in float32.
 Tensors: `<name>dq`, `dq.norm`, `uq`, `dkv`, `dkv.norm`, `uk`, `uv`, `o`.
 """
@@ -43,8 +44,9 @@ class LatentAttention(Part):
         self.D = self.dr + self.kv_rank                  # the cached key row: [k_rot | c]
         if self.dr % 2:
             raise ValueError(f"{self.dr} turning dims are not even")
-        if not 1 <= self.D <= 256:
-            raise ValueError(f"a cached row of {self.dr} + {self.kv_rank} dims; the kernels take up to 256")
+        if not (1 <= self.D <= 576 and self.kv_rank <= 256):
+            raise ValueError(f"a cached row of {self.dr} + {self.kv_rank} dims; the kernels take up to 576, with a "
+                             f"latent of up to 256")
         self.down: Optional[Linear] = None
         self.uq: Optional[Linear] = None
         self.o: Optional[Linear] = None
@@ -85,25 +87,17 @@ class LatentAttention(Part):
         N, H, D, rank, dr, dn = x.shape[0], self.H, self.D, self.kv_rank, self.dr, self.dn
         down = self.down(ctx, x, "la_down")                                  # [c_q raw | c raw | k_rot raw]
         cq = ctx.buffers.take("la_cq", N, (self.q_rank,), ctx.dtype)
-        # the rotation kernel's input: H query heads [q_rot | q in latent space], the key head [k_rot | c], the value c
-        rows = ctx.buffers.take("la_rows", N, (H * D + D + rank,), ctx.dtype)
-        ops.segment_norm(down, [
-            (0, self.q_rank, self.q_gain, [(cq, 0)]),
-            (self.q_rank, rank, self.kv_gain, [(rows, H * D + dr), (rows, H * D + D)]),
-            (self.q_rank + rank, dr, None, [(rows, H * D)]),
-        ] if dr else [
-            (0, self.q_rank, self.q_gain, [(cq, 0)]),
-            (self.q_rank, rank, self.kv_gain, [(rows, H * D + dr), (rows, H * D + D)]),
-        ], self.eps)
+        ops.segment_norm(down, [(0, self.q_rank, self.q_gain, [(cq, 0)])], self.eps)
         qf = self.uq(ctx, cq, "la_q")                                        # per head [turning | not turning]
-        ops.head_matmul(rows, dr, D, qf, dr, dn + dr, self.uk, H, transposed=True, carry=dr)
+        # the query heads as the attention kernel reads them: [q_rot | q carried into the latent space]
         q = ctx.buffers.take("la_qr", N, (H * D,), ctx.dtype)
+        ops.head_matmul(q, dr, D, qf, dr, dn + dr, self.uk, H, transposed=True, carry=dr)
         k_pool, v_pool = cache.pools()
         table = cache.block_table()
         inv_freq, rotary_dim = self.position.tables(x.device)
-        ops.qk_norm_rope_kvwrite(rows, q, k_pool, v_pool, None, None, inv_freq, rotary_dim, ctx.positions,
-                                 ctx.token_rows, table, 0.0, H, 1, D, value_dim=rank,
-                                 neighbours=self.position.neighbours, magnitude=getattr(self.position, "magnitude", 1.0))
+        ops.latent_write(down, self.q_rank, self.q_rank + rank, rank, rotary_dim, self.kv_gain, self.eps, q, H,
+                         inv_freq, self.position.neighbours, getattr(self.position, "magnitude", 1.0),
+                         ctx.positions, ctx.token_rows, table, k_pool, v_pool)
         lat = ctx.buffers.take("la_lat", N, (H * rank,), ctx.dtype)
         if (not ctx.all_decode and N >= 4 * ctx.num_seqs
                 and ops.attention_bias_tile_supports(H, 1, D, rank, ctx.dtype)):

@@ -28,6 +28,7 @@ from .linear import Linear
 
 class TalkingAttention(Part):
     out_buffer = "branch"
+    shared_projection = True       # a mixer that holds this one may make the projections (they must start its rows)
 
     def __init__(self, spec, name):
         super().__init__(spec, name)
@@ -70,7 +71,7 @@ class TalkingAttention(Part):
         return CacheNeeds(paged=PagedKVSpec(self.G, self.dk, self.window, None if self.dv == self.dk else self.dv))
 
     def streamed_weights(self):
-        return [self.proj.weight, self.o.weight]
+        return [*([self.proj.weight] if self.proj is not None else []), self.o.weight]
 
     def partitions(self, ctx, N: int, max_len: int) -> int:
         """Into how many shares a decode step cuts each token's keys: about two blocks an SM, at least 128 keys a
@@ -79,9 +80,14 @@ class TalkingAttention(Part):
         span = min(self.window or max_len, max_len)
         return max(1, min(32, (2 * ctx.num_sms) // max(1, N), -(-span // 128)))
 
-    def forward(self, ctx, x: torch.Tensor, cache) -> Branch:
+    def forward(self, ctx, x: torch.Tensor, cache, proj=None) -> Branch:
         N = x.shape[0]
-        proj = self.proj(ctx, x, "ta_proj")
+        if proj is None:
+            proj = self.proj(ctx, x, "ta_proj")
+        else:
+            proj, first = proj                   # a wider product made outside; this mixer's columns come first
+            if first != 0:
+                raise ValueError("the rotation kernel reads its heads from the start of a row")
         q = ctx.buffers.take("ta_q", N, (self.Cq,), ctx.dtype)
         k_pool, v_pool = cache.pools()
         table = cache.block_table()
@@ -91,7 +97,7 @@ class TalkingAttention(Part):
             self.H, self.G, self.dk, value_dim=self.dv, row_width=proj.shape[1],
             neighbours=self.position.neighbours, magnitude=getattr(self.position, "magnitude", 1.0))
         attn = ctx.buffers.take("ta_attn", N, (self.H * self.dv,), ctx.dtype)
-        gate = proj[:, self.Cq + self.Ckv:] if self.gate else None
+        gate = proj[:, self.Cq + self.Ckv:self.Cq + self.Ckv + self.Cg] if self.gate else None
         if ctx.all_decode:
             NP, part_o, part_ml = self.partitions(ctx, N, cache.manager.max_len), None, None
             if NP > 1:
