@@ -72,7 +72,8 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (int i = tid; i < H * H; i += THREADS) talk_s[i] = a.talk[i];     // weights: before the wait
     sb::pdl_wait();
-    int r = 0, ti = blockIdx.x;
+    // tiles are served last first: a request's late tiles see the most keys and should not start last
+    int r = 0, ti = (int)(gridDim.x - 1 - blockIdx.x);
     for (; r < a.R; ++r) {
         const int nt = (a.seq_starts[r + 1] - a.seq_starts[r] + QT - 1) / QT;
         if (ti < nt) break;
@@ -120,17 +121,24 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
                 for (int j = 0; j < RGRP; ++j) dot[j] = 0.f;
                 if (have) {
                     if (vec_keys) {
-                        for (int d = 0; d < Dk; d += VEC) {
-                            Vec16<T> kv;
-                            kv.load(kr + d);
+                        for (int d0 = 0; d0 < Dk; d0 += 4 * VEC) {          // four 16-byte pieces in flight
+                            Vec16<T> kv[4];
 #pragma unroll
-                            for (int e = 0; e < VEC; e += 4) {
-                                const float k0 = kv.get(e), k1 = kv.get(e + 1), k2 = kv.get(e + 2), k3 = kv.get(e + 3);
+                            for (int u = 0; u < 4; ++u)
+                                if (d0 + u * VEC < Dk) kv[u].load(kr + d0 + u * VEC);
 #pragma unroll
-                                for (int j = 0; j < RGRP; ++j) {
-                                    if (j < rn) {
-                                        const float4 qv = *reinterpret_cast<const float4*>(qrow + j * DkP + d + e);
-                                        dot[j] = fmaf(qv.x, k0, fmaf(qv.y, k1, fmaf(qv.z, k2, fmaf(qv.w, k3, dot[j]))));
+                            for (int u = 0; u < 4; ++u) {
+                                const int d = d0 + u * VEC;
+                                if (d >= Dk) break;
+#pragma unroll
+                                for (int e = 0; e < VEC; e += 4) {
+                                    const float k0 = kv[u].get(e), k1 = kv[u].get(e + 1), k2 = kv[u].get(e + 2), k3 = kv[u].get(e + 3);
+#pragma unroll
+                                    for (int j = 0; j < RGRP; ++j) {
+                                        if (j < rn) {
+                                            const float4 qv = *reinterpret_cast<const float4*>(qrow + j * DkP + d + e);
+                                            dot[j] = fmaf(qv.x, k0, fmaf(qv.y, k1, fmaf(qv.z, k2, fmaf(qv.w, k3, dot[j]))));
+                                        }
                                     }
                                 }
                             }

@@ -42,10 +42,35 @@ struct HyperArgs {
     int s, d, write_streams, has_branch;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(256) hyper_fold_norm_kernel(HyperArgs a) {
+// E consecutive columns a thread and step: 4 (16-byte accesses; d a multiple of 4 and aligned rows) or 1.
+// Everything a column needs (its streams, every partial sum of both branches, the bias) is loaded before
+// anything is added, so a row costs one or two round trips to memory however many streams and parts there are.
+template <int E> struct Pack;
+template <> struct Pack<1> {
+    float v[1];
+    __device__ __forceinline__ void load(const float* p) { v[0] = __ldg(p); }
+    __device__ __forceinline__ void load_rw(const float* p) { v[0] = *p; }
+    __device__ __forceinline__ void store(float* p) const { *p = v[0]; }
+};
+template <> struct Pack<4> {
+    float v[4];
+    __device__ __forceinline__ void load(const float* p) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(p));
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    __device__ __forceinline__ void load_rw(const float* p) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+
+// SM_: most streams the instance takes; PA, PB: partial sums of the first and second branch whose loads are in
+// flight at once (more are added one by one afterwards).
+template <typename T, int E, int SM_, int PA, int PB>
+__global__ void __launch_bounds__(E == 4 ? 256 : 1024) hyper_fold_norm_kernel(HyperArgs a) {
     sb::pdl_launch_dependents();
-    extern __shared__ float urow[];         // d floats
+    extern __shared__ __align__(16) float urow[];         // d floats
     __shared__ float scratch[33];
     __shared__ float c_mix[SMAX * SMAX], c_out[SMAX], c_in[SMAX];
     const int s = a.s, d = a.d, m = blockIdx.x;
@@ -60,82 +85,114 @@ __global__ void __launch_bounds__(256) hyper_fold_norm_kernel(HyperArgs a) {
     const int r = a.row_index ? a.row_index[m] : m;
     float* xs = a.streams + (size_t)r * s * d;
     float total = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float x[SMAX];
+    for (int i = threadIdx.x * E; i < d; i += blockDim.x * E) {
+        Pack<E> x[SM_], pa[PA], pb[PB], bias;
+        // ---- every load of the column first
         if (a.init) {
-            const float v = a.init[(size_t)r * d + i];
+            x[0].load(a.init + (size_t)r * d + i);
 #pragma unroll
-            for (int t = 0; t < SMAX; ++t) x[t] = v;
+            for (int t = 1; t < SM_; ++t) x[t] = x[0];
         } else {
 #pragma unroll
-            for (int t = 0; t < SMAX; ++t) x[t] = t < s ? xs[(size_t)t * d + i] : 0.f;
+            for (int t = 0; t < SM_; ++t)
+                if (t < s) x[t].load_rw(xs + (size_t)t * d + i);
         }
         if (a.has_branch) {
-            float ya = 0.f, yb = 0.f;
-            for (int p0 = 0; p0 < a.SA; p0 += 8) {                 // eight loads in flight, added in order
-                float v[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (p0 + j < a.SA) v[j] = __ldg(a.a + (size_t)(p0 + j) * a.stride_a + (size_t)r * d + i);
+            for (int j = 0; j < PA; ++j)
+                if (j < a.SA) pa[j].load(a.a + (size_t)j * a.stride_a + (size_t)r * d + i);
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (p0 + j < a.SA) ya += v[j];
-            }
-            if (a.bias) ya += a.bias[i];
-            for (int p0 = 0; p0 < a.SB; p0 += 8) {
-                float v[8];
+            for (int j = 0; j < PB; ++j)
+                if (j < a.SB) pb[j].load(a.b + (size_t)j * a.stride_b + (size_t)r * d + i);
+            if (a.bias) bias.load(a.bias + i);
+        }
+        // ---- then the arithmetic, element by element of the pack
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (p0 + j < a.SB) v[j] = __ldg(a.b + (size_t)(p0 + j) * a.stride_b + (size_t)r * d + i);
+        for (int e = 0; e < E; ++e) {
+            float xv[SM_];
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (p0 + j < a.SB) yb += v[j];
-            }
-            const float y = a.SB > 0 ? a.scale_a * ya + a.scale_b * yb : a.scale_a * ya;
-            float nx[SMAX];
+            for (int t = 0; t < SM_; ++t) xv[t] = t < s ? x[t].v[e] : 0.f;
+            if (a.has_branch) {
+                float ya = 0.f, yb = 0.f;
 #pragma unroll
-            for (int t = 0; t < SMAX; ++t) {
-                float v = 0.f;
-                if (t < s) {
+                for (int j = 0; j < PA; ++j)
+                    if (j < a.SA) ya += pa[j].v[e];
+                for (int j = PA; j < a.SA; ++j) ya += __ldg(a.a + (size_t)j * a.stride_a + (size_t)r * d + i + e);
+                if (a.bias) ya += bias.v[e];
 #pragma unroll
-                    for (int f = 0; f < SMAX; ++f)
-                        if (f < s) v = fmaf(c_mix[f * s + t], x[f], v);
-                    v = fmaf(c_out[t], y, v);
+                for (int j = 0; j < PB; ++j)
+                    if (j < a.SB) yb += pb[j].v[e];
+                for (int j = PB; j < a.SB; ++j) yb += __ldg(a.b + (size_t)j * a.stride_b + (size_t)r * d + i + e);
+                const float y = a.SB > 0 ? a.scale_a * ya + a.scale_b * yb : a.scale_a * ya;
+                float nx[SM_];
+#pragma unroll
+                for (int t = 0; t < SM_; ++t) {
+                    float v = 0.f;
+                    if (t < s) {
+#pragma unroll
+                        for (int f = 0; f < SM_; ++f)
+                            if (f < s) v = fmaf(c_mix[f * s + t], xv[f], v);
+                        v = fmaf(c_out[t], y, v);
+                    }
+                    nx[t] = v;
                 }
-                nx[t] = v;
-            }
 #pragma unroll
-            for (int t = 0; t < SMAX; ++t) x[t] = nx[t];
+                for (int t = 0; t < SM_; ++t) { xv[t] = nx[t]; x[t].v[e] = nx[t]; }
+            }
+            float u = 0.f;
+#pragma unroll
+            for (int t = 0; t < SM_; ++t)
+                if (t < s) u = fmaf(c_in[t], xv[t], u);
+            urow[i + e] = u;
+            total += u;
+            if (a.read_out) a.read_out[(size_t)m * d + i + e] = u;
         }
         if (a.write_streams) {
 #pragma unroll
-            for (int t = 0; t < SMAX; ++t)
-                if (t < s) xs[(size_t)t * d + i] = x[t];
+            for (int t = 0; t < SM_; ++t)
+                if (t < s) x[t].store(xs + (size_t)t * d + i);
         }
-        float u = 0.f;
-#pragma unroll
-        for (int t = 0; t < SMAX; ++t)
-            if (t < s) u = fmaf(c_in[t], x[t], u);
-        urow[i] = u;
-        total += u;
-        if (a.read_out) a.read_out[(size_t)m * d + i] = u;
     }
     if (a.out == nullptr) return;
     T* o = (T*)a.out + (size_t)m * d;
     if (a.gain == nullptr) {
+        __syncthreads();
         for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<T>(urow[i]);
         return;
     }
     float mean = 0.f;
     if (a.center) mean = block_sum(total, scratch) / (float)d;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = urow[i] - mean;
-        ss += v * v;
+    for (int i = threadIdx.x * E; i < d; i += blockDim.x * E) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float v = urow[i + e] - mean;
+            ss += v * v;
+        }
     }
     const float var = block_sum(ss, scratch) / (float)d;
     const float rinv = 1.0f / sqrtf(var + a.eps);
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<T>((urow[i] - mean) * rinv * a.gain[i]);
+}
+
+template <typename T, int E, int SM_, int PA, int PB>
+cudaError_t launch_one(const HyperArgs& h, int M, int threads, size_t smem, cudaStream_t stream) {
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(hyper_fold_norm_kernel<T, E, SM_, PA, PB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return sb::launch(hyper_fold_norm_kernel<T, E, SM_, PA, PB>, dim3(M), dim3(threads), smem, stream, h);
+}
+
+template <typename T>
+cudaError_t launch_hyper(const HyperArgs& h, int M, size_t smem, cudaStream_t stream) {
+    auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = h.d % 4 == 0 && h.stride_a % 4 == 0 && h.stride_b % 4 == 0 && aligned(h.streams) && aligned(h.init) &&
+                     aligned(h.a) && aligned(h.b) && aligned(h.bias);
+    auto round32 = [](int n, int most) { n = ((n + 31) / 32) * 32; return n > most ? most : (n < 32 ? 32 : n); };
+    // Few rows (a decode step, the head's rows): a thread a column and every partial sum in flight, so that a row
+    // is one round of loads.  Many rows: 256 threads; 16-byte packs where there are at most four streams.
+    if (M <= 512) return launch_one<T, 1, SMAX, 16, 16>(h, M, round32(h.d, 1024), smem, stream);
+    if (vec && h.s <= 4) return launch_one<T, 4, 4, 4, 4>(h, M, round32(h.d / 4, 256), smem, stream);
+    return launch_one<T, 1, SMAX, 8, 8>(h, M, round32(h.d, 256), smem, stream);
 }
 
 }  // namespace
@@ -159,18 +216,8 @@ extern "C" int sb_hyper_fold_norm(float* streams, const float* init, int s, int 
     h.read_out = read_out; h.row_index = row_index; h.s = s; h.d = d;
     h.has_branch = SA > 0 || bias != nullptr;
     h.write_streams = row_index == nullptr && (h.has_branch || init != nullptr);
-    int threads = ((d + 31) / 32) * 32;
-    if (threads > 256) threads = 256;
-    if (out_dtype == SB_F32) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(hyper_fold_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        sb::launch(hyper_fold_norm_kernel<float>, dim3(M), dim3(threads), smem, stream, h);
-    } else if (out_dtype == SB_BF16) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(hyper_fold_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        sb::launch(hyper_fold_norm_kernel<__nv_bfloat16>, dim3(M), dim3(threads), smem, stream, h);
-    } else {
-        SB_REQUIRE(false, "hyper_fold_norm: unknown dtype %d", out_dtype);
-    }
+    if (out_dtype == SB_F32) launch_hyper<float>(h, M, smem, stream);
+    else if (out_dtype == SB_BF16) launch_hyper<__nv_bfloat16>(h, M, smem, stream);
+    else SB_REQUIRE(false, "hyper_fold_norm: unknown dtype %d", out_dtype);
     SB_LAUNCH_CHECK();
 }

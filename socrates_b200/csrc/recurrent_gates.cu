@@ -126,14 +126,23 @@ constexpr int COLS = 8;        // columns of a block
 constexpr int TB = 16;         // tokens staged at a time
 constexpr int GTHREADS = RG * COLS;
 
+// The walk over a request's tokens is serial, so nothing in it may wait for memory: while the threads walk
+// the 16 tokens of one chunk, the raw gate and query values of the NEXT chunk are already on their way into
+// registers; gates, lower bound and SiLU are applied when they are moved to shared memory.
 template <typename T, int DR>
 __global__ void __launch_bounds__(GTHREADS) gla_kernel(GlaArgs a) {
     sb::pdl_launch_dependents();
     constexpr int DP = RG * DR;                       // padded key dims
+    constexpr int NE = TB * DP / GTHREADS;            // (token, key dim) pairs a thread stages per chunk
     __shared__ float fs[TB][DP + 4], qs[TB][DP + 4], vs[TB][COLS], os[TB][COLS];
+    __shared__ float low_s[DP], fb_s[DP];
     const int h = blockIdx.x, r = blockIdx.y, c0 = blockIdx.z * COLS;
     const int tid = threadIdx.x, rg = tid & (RG - 1), cj = tid / RG, j = c0 + cj;
     const int D = a.D, Dv = a.Dv, H = a.H;
+    for (int d = tid; d < DP; d += GTHREADS) {        // constants of the model: before the wait
+        low_s[d] = (d < D && a.lower) ? a.lower[h * D + d] : 0.f;
+        fb_s[d] = (d < D && a.f_bias) ? a.f_bias[h * D + d] : 0.f;
+    }
     sb::pdl_wait();
     const int t0 = a.seq_starts[r], t1 = a.seq_starts[r + 1];
     if (t0 >= t1) return;
@@ -146,28 +155,39 @@ __global__ void __launch_bounds__(GTHREADS) gla_kernel(GlaArgs a) {
         const int i = rg + RG * ii;                   // thread rg owns rows rg, rg + 16, ...
         S[ii] = (col && i < D) ? sp[(size_t)i * Dv] : 0.f;
     }
+    float rf[NE], rq[NE], rv;
+    auto fetch = [&](int tc) {
+#pragma unroll
+        for (int k = 0; k < NE; ++k) {
+            const int i = tid + k * GTHREADS, tt = i / DP, d = i - tt * DP;
+            rf[k] = rq[k] = 0.f;
+            if (d < D && tc + tt < t1) {
+                const T* row = proj + (size_t)(tc + tt) * a.stride + h * D + d;
+                rf[k] = to_float(row[a.f_off]);
+                rq[k] = to_float(row[a.q_off]);
+            }
+        }
+        const int tt = tid / COLS, c = tid - tt * COLS;            // TB * COLS = GTHREADS: one value a thread
+        rv = (c0 + c < Dv && tc + tt < t1) ? to_float(proj[(size_t)(tc + tt) * a.stride + a.v_off + h * Dv + c0 + c]) : 0.f;
+    };
+    fetch(t0);
     for (int tc = t0; tc < t1; tc += TB) {
         const int nt = min(TB, t1 - tc);
-        __syncthreads();
-        for (int i = tid; i < nt * DP; i += GTHREADS) {
-            const int tt = i / DP, d = i - tt * DP;
-            float f = 1.f, q = 0.f;                   // rows past D keep their zero state and read nothing
-            if (d < D) {
-                const T* row = proj + (size_t)(tc + tt) * a.stride;
-                const int ch = h * D + d;
-                const float l = a.lower ? a.lower[ch] : 0.f;
-                f = l + (1.0f - l) * sigmoidf_(to_float(row[a.f_off + ch]) + (a.f_bias ? a.f_bias[ch] : 0.f));
-                const float z = to_float(row[a.q_off + ch]);
-                q = z * sigmoidf_(z);
-            }
-            fs[tt][d] = f;
-            qs[tt][d] = q;
+        __syncthreads();                              // the walk over the chunk before is over
+#pragma unroll
+        for (int k = 0; k < NE; ++k) {
+            const int i = tid + k * GTHREADS, tt = i / DP, d = i - tt * DP;
+            const float l = low_s[d];
+            fs[tt][d] = d < D ? l + (1.0f - l) * sigmoidf_(rf[k] + fb_s[d]) : 1.f;      // rows past D keep a zero state
+            qs[tt][d] = rq[k] * sigmoidf_(rq[k]);
         }
-        for (int i = tid; i < nt * COLS; i += GTHREADS) {
-            const int tt = i / COLS, c = i - tt * COLS;
-            vs[tt][c] = c0 + c < Dv ? to_float(proj[(size_t)(tc + tt) * a.stride + a.v_off + h * Dv + c0 + c]) : 0.f;
-        }
+        vs[tid / COLS][tid % COLS] = rv;
         __syncthreads();
+        if (tc + TB < t1) fetch(tc + TB);             // in flight while the chunk is walked
+        // the state of one token feeds the next through one multiply-add only; the dot products and their shuffles
+        // of four tokens run side by side (the chunk's tail past nt holds f = 1, v = q = 0 from an earlier chunk
+        // or garbage that is never written out, and the state is walked over real tokens only)
+#pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
             const float v = vs[tt][cj];
             float o = 0.f;
@@ -182,9 +202,9 @@ __global__ void __launch_bounds__(GTHREADS) gla_kernel(GlaArgs a) {
             if (rg == 0) os[tt][cj] = o;
         }
         __syncthreads();
-        for (int i = tid; i < nt * COLS; i += GTHREADS) {
-            const int tt = i / COLS, c = i - tt * COLS;
-            if (c0 + c < Dv) a.raw_o[(size_t)(tc + tt) * H * Dv + h * Dv + c0 + c] = os[tt][c];
+        {
+            const int tt = tid / COLS, c = tid - tt * COLS;
+            if (tt < nt && c0 + c < Dv) a.raw_o[(size_t)(tc + tt) * H * Dv + h * Dv + c0 + c] = os[tt][c];
         }
     }
 #pragma unroll
