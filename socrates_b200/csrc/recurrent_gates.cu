@@ -119,6 +119,12 @@ struct GlaArgs {
     const int* seq_rows;
     int H, D, Dv;
     float eps;
+    // Long portions are cut into `segs` segments that run side by side (the recurrence is linear in S with a
+    // diagonal decay): mode 1 walks every segment from a zero state and leaves its end state and the product of
+    // its forget gates in `seg_scratch`; mode 2 joins what the earlier segments left, in order, walks again
+    // and writes the outputs.  Mode 0: one segment, one walk.
+    int mode, segs;
+    float* seg_scratch;        // [R, segs + 1, H, D, Dv + 1]: per segment the end state and (last column) the gate product; slot `segs`: the state at the start
 };
 
 constexpr int RG = 16;         // threads that share a column of the state
@@ -136,7 +142,7 @@ __global__ void __launch_bounds__(GTHREADS) gla_kernel(GlaArgs a) {
     constexpr int NE = TB * DP / GTHREADS;            // (token, key dim) pairs a thread stages per chunk
     __shared__ float fs[TB][DP + 4], qs[TB][DP + 4], vs[TB][COLS], os[TB][COLS];
     __shared__ float low_s[DP], fb_s[DP];
-    const int h = blockIdx.x, r = blockIdx.y, c0 = blockIdx.z * COLS;
+    const int h = blockIdx.x, r = blockIdx.y / a.segs, seg = blockIdx.y - r * a.segs, c0 = blockIdx.z * COLS;
     const int tid = threadIdx.x, rg = tid & (RG - 1), cj = tid / RG, j = c0 + cj;
     const int D = a.D, Dv = a.Dv, H = a.H;
     for (int d = tid; d < DP; d += GTHREADS) {        // constants of the model: before the wait
@@ -144,16 +150,35 @@ __global__ void __launch_bounds__(GTHREADS) gla_kernel(GlaArgs a) {
         fb_s[d] = (d < D && a.f_bias) ? a.f_bias[h * D + d] : 0.f;
     }
     sb::pdl_wait();
-    const int t0 = a.seq_starts[r], t1 = a.seq_starts[r + 1];
-    if (t0 >= t1) return;
+    const int r0 = a.seq_starts[r], r1 = a.seq_starts[r + 1];
+    if (r0 >= r1) return;
+    const int per = (r1 - r0 + a.segs - 1) / a.segs;
+    const int t0 = min(r1, r0 + seg * per), t1 = min(r1, t0 + per);      // this block's tokens
     const T* proj = (const T*)a.proj;
     const bool col = j < Dv;
     float* sp = a.state + ((size_t)a.seq_rows[r] * H + h) * D * Dv + j;
-    float S[DR];
+    const size_t SW = (size_t)Dv + 1;                                    // a scratch row: Dv state values, then the gate product
+    float* seg_base = a.seg_scratch + ((size_t)r * (a.segs + 1) * H + h) * D * SW;
+    const size_t seg_stride = (size_t)H * D * SW;
+    float S[DR], A[DR];
 #pragma unroll
     for (int ii = 0; ii < DR; ++ii) {
         const int i = rg + RG * ii;                   // thread rg owns rows rg, rg + 16, ...
-        S[ii] = (col && i < D) ? sp[(size_t)i * Dv] : 0.f;
+        const bool live = col && i < D;
+        A[ii] = 1.f;
+        S[ii] = 0.f;
+        if (a.mode == 0) {
+            S[ii] = live ? sp[(size_t)i * Dv] : 0.f;
+        } else if (a.mode == 1) {
+            if (seg == 0 && live) seg_base[a.segs * seg_stride + (size_t)i * SW + j] = sp[(size_t)i * Dv];     // kept for mode 2
+        } else if (live) {
+            float v = seg_base[a.segs * seg_stride + (size_t)i * SW + j];
+            for (int k = 0; k < seg; ++k) {
+                const float* sk = seg_base + k * seg_stride + (size_t)i * SW;
+                v = fmaf(sk[Dv], v, sk[j]);
+            }
+            S[ii] = v;
+        }
     }
     float rf[NE], rq[NE], rv;
     auto fetch = [&](int tc) {
@@ -195,14 +220,16 @@ __global__ void __launch_bounds__(GTHREADS) gla_kernel(GlaArgs a) {
             for (int ii = 0; ii < DR; ++ii) {
                 const float f = fs[tt][rg + RG * ii];
                 S[ii] = fmaf(f, S[ii] - v, v);        // f S + (1 - f) v
+                A[ii] *= f;
                 o = fmaf(S[ii], qs[tt][rg + RG * ii], o);
             }
+            if (a.mode == 1) continue;                // only the end state and the gate product are wanted
 #pragma unroll
             for (int sh = 1; sh < RG; sh <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
             if (rg == 0) os[tt][cj] = o;
         }
         __syncthreads();
-        {
+        if (a.mode != 1) {
             const int tt = tid / COLS, c = tid - tt * COLS;
             if (tt < nt && c0 + c < Dv) a.raw_o[(size_t)(tc + tt) * H * Dv + h * Dv + c0 + c] = os[tt][c];
         }
@@ -210,7 +237,14 @@ __global__ void __launch_bounds__(GTHREADS) gla_kernel(GlaArgs a) {
 #pragma unroll
     for (int ii = 0; ii < DR; ++ii) {
         const int i = rg + RG * ii;
-        if (col && i < D) sp[(size_t)i * Dv] = S[ii];
+        if (!(col && i < D)) continue;
+        if (a.mode == 1) {
+            float* sk = seg_base + seg * seg_stride + (size_t)i * SW;
+            sk[j] = S[ii];
+            if (j == 0) sk[Dv] = A[ii];               // the same in every column; column 0 writes it
+        } else if (seg == a.segs - 1) {
+            sp[(size_t)i * Dv] = S[ii];               // the last segment leaves the request's state
+        }
     }
 }
 
@@ -232,11 +266,14 @@ __global__ void __launch_bounds__(128) gla_out_kernel(GlaArgs a, int N) {
 }
 
 template <typename T>
-int launch_gla(const GlaArgs& a, int R, int N, cudaStream_t stream) {
-    const dim3 grid(a.H, R, (a.Dv + COLS - 1) / COLS);
-    if (a.D <= RG * 4) sb::launch(gla_kernel<T, 4>, grid, dim3(GTHREADS), 0, stream, a);
-    else if (a.D <= RG * 8) sb::launch(gla_kernel<T, 8>, grid, dim3(GTHREADS), 0, stream, a);
-    else sb::launch(gla_kernel<T, 16>, grid, dim3(GTHREADS), 0, stream, a);
+int launch_gla(GlaArgs a, int R, int N, cudaStream_t stream) {
+    const dim3 grid(a.H, R * a.segs, (a.Dv + COLS - 1) / COLS);
+    for (int mode = a.segs > 1 ? 1 : 0; mode <= (a.segs > 1 ? 2 : 0); ++mode) {
+        a.mode = mode;
+        if (a.D <= RG * 4) sb::launch(gla_kernel<T, 4>, grid, dim3(GTHREADS), 0, stream, a);
+        else if (a.D <= RG * 8) sb::launch(gla_kernel<T, 8>, grid, dim3(GTHREADS), 0, stream, a);
+        else sb::launch(gla_kernel<T, 16>, grid, dim3(GTHREADS), 0, stream, a);
+    }
     sb::launch(gla_out_kernel<T>, dim3((N * a.H + 3) / 4), dim3(128), 0, stream, a, N);
     SB_LAUNCH_CHECK();
 }
@@ -265,20 +302,30 @@ extern "C" int sb_min_gru(void* out, const void* proj, long long stride, const f
 
 extern "C" int sb_gated_linear_attention_supports(int D, int Dv) { return D >= 1 && D <= 256 && Dv >= 1; }
 
+// Segments a request's tokens are cut into when the longest request brings at most `longest` tokens: at least
+// 128 tokens a segment, at most 16 segments.
+extern "C" int sb_gated_linear_attention_segments(int longest) {
+    const int s = (longest + 127) / 128;
+    return s < 1 ? 1 : (s > 16 ? 16 : s);
+}
+
 extern "C" int sb_gated_linear_attention(void* out, const void* proj, long long stride, int q_off, int f_off,
                                          int v_off, const float* f_bias, const float* lower, const float* norm_w,
                                          float* state, const int* seq_starts, const int* seq_rows, int R, int H,
-                                         int D, int Dv, float eps, int dtype, float* raw_o, int N,
-                                         cudaStream_t stream) {
+                                         int D, int Dv, float eps, int dtype, float* raw_o, int N, int segs,
+                                         float* seg_scratch, cudaStream_t stream) {
+    SB_REQUIRE(segs >= 1 && segs <= 16 && (segs == 1 || seg_scratch != nullptr),
+               "gated_linear_attention: %d segments (1 to 16; more than one needs scratch)", segs);
     SB_REQUIRE(R >= 0 && H > 0 && sb_gated_linear_attention_supports(D, Dv),
                "gated_linear_attention: %d heads of %d (keys, at most 256) and %d (values) dims", H, D, Dv);
-    SB_REQUIRE(R <= 65535 && (Dv + COLS - 1) / COLS <= 65535, "gated_linear_attention: %d requests exceed one launch", R);
+    SB_REQUIRE(R * segs <= 65535 && (Dv + COLS - 1) / COLS <= 65535, "gated_linear_attention: %d requests exceed one launch", R);
     SB_REQUIRE(raw_o != nullptr && N >= 0, "gated_linear_attention: scratch for %d tokens is missing", N);
     if (R == 0 || N == 0) return 0;
     GlaArgs a;
     a.proj = proj; a.stride = stride; a.q_off = q_off; a.f_off = f_off; a.v_off = v_off; a.f_bias = f_bias;
     a.lower = lower; a.norm_w = norm_w; a.state = state; a.out = out; a.raw_o = raw_o;
     a.seq_starts = seq_starts; a.seq_rows = seq_rows; a.H = H; a.D = D; a.Dv = Dv; a.eps = eps;
+    a.mode = 0; a.segs = segs; a.seg_scratch = seg_scratch;
     if (dtype == SB_F32) return launch_gla<float>(a, R, N, stream);
     if (dtype == SB_BF16) return launch_gla<__nv_bfloat16>(a, R, N, stream);
     SB_REQUIRE(false, "gated_linear_attention: unknown dtype %d", dtype);

@@ -73,7 +73,8 @@ _SIGNATURES = {
     "sb_hyper_fold_norm": [P, P, I, I, P, I, LL, F, P, I, LL, F, P, P, P, F, P, P, F, I, P, P, P, I, I, P],
     "sb_min_gru": [P, P, LL, P, P, P, P, P, I, I, I, I, P],
     "sb_gated_linear_attention_supports": [I, I],
-    "sb_gated_linear_attention": [P, P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, F, I, P, I, P],
+    "sb_gated_linear_attention_segments": [I],
+    "sb_gated_linear_attention": [P, P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, F, I, P, I, I, P, P],
     "sb_glu_clamp": [P, P, P, I, LL, P, P, I, I, F, F, F, I, P],
     "sb_scale": [P, LL, F, P],
     "sb_segment_norm": [P, LL, I, P, P, P, P, P, P, P, P, P, F, I, I, P],

@@ -1151,11 +1151,15 @@ def gated_linear_attention_supports(key_dim: int, value_dim: int) -> bool:
 def gated_linear_attention(out: torch.Tensor, proj: torch.Tensor, offsets: Tuple[int, int, int],
                            f_bias: Optional[torch.Tensor], lower: Optional[torch.Tensor], norm_w: torch.Tensor,
                            state: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor, num_heads: int,
-                           key_dim: int, value_dim: int, eps: float, scratch: torch.Tensor) -> None:
+                           key_dim: int, value_dim: int, eps: float, scratch: torch.Tensor,
+                           longest: Optional[int] = None, seg_scratch: Optional[torch.Tensor] = None) -> None:
     """Linear attention whose forget gate also decides what is written, token after token of every request:
     q = silu(proj_q); f = lower + (1 - lower) * sigmoid(proj_f + f_bias); S <- diag(f) S + (1 - f) v^T; o = S^T q;
     out = o / sqrt(mean(o^2) + eps) * norm_w per head.  `offsets` = columns where q (H*D), f (H*D) and v (H*Dv)
-    begin in proj; state float32 [rows, H, D, Dv]; scratch float32 [N, H*Dv] (the raw o)."""
+    begin in proj; state float32 [rows, H, D, Dv]; scratch float32 [N, H*Dv] (the raw o).
+    `longest`: an upper bound of the tokens one request brings (default N - R + 1).  Long portions are cut into
+    `gated_linear_attention_segments(longest)` segments that run side by side and are joined in order; with more
+    than one, `seg_scratch` float32 of `gated_linear_attention_seg_scratch(R, longest, H, D, Dv)` values is needed."""
     H, D, Dv = num_heads, key_dim, value_dim
     N = out.shape[0]
     _want(out, "out", None, (N, H * Dv))
@@ -1177,11 +1181,30 @@ def gated_linear_attention(out: torch.Tensor, proj: torch.Tensor, offsets: Tuple
     R = seq_rows.numel()
     _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
     _want(seq_rows, "seq_rows", torch.int32, (R,))
+    longest = N - R + 1 if longest is None else int(longest)
+    segs = gated_linear_attention_segments(longest)
+    if segs > 1:
+        if seg_scratch is None:
+            raise KernelError(f"{segs} segments need seg_scratch")
+        _want(seg_scratch, "seg_scratch", torch.float32)
+        if seg_scratch.numel() < gated_linear_attention_seg_scratch(R, longest, H, D, Dv):
+            raise KernelError("seg_scratch is too small")
     lib = library()
     check(lib, lib.sb_gated_linear_attention(_ptr(out), _ptr(proj), proj.stride(0), q_off, f_off, v_off, _ptr(f_bias),
                                              _ptr(lower), _ptr(norm_w), _ptr(state), _ptr(seq_starts), _ptr(seq_rows),
-                                             R, H, D, Dv, float(eps), _code(out.dtype), _ptr(scratch), N, _stream()),
-          "gated_linear_attention", kernels=2)
+                                             R, H, D, Dv, float(eps), _code(out.dtype), _ptr(scratch), N, segs,
+                                             _ptr(seg_scratch) if segs > 1 else None, _stream()),
+          "gated_linear_attention", kernels=3 if segs > 1 else 2)
+
+
+def gated_linear_attention_segments(longest: int) -> int:
+    return int(library().sb_gated_linear_attention_segments(int(longest)))
+
+
+def gated_linear_attention_seg_scratch(R: int, longest: int, H: int, D: int, Dv: int) -> int:
+    """float32 values of scratch the segments of `gated_linear_attention` need (0 with one segment)."""
+    segs = gated_linear_attention_segments(longest)
+    return 0 if segs == 1 else R * (segs + 1) * H * D * (Dv + 1)
 
 
 def glu_clamp(out: torch.Tensor, x: torch.Tensor, bias_gate: Optional[torch.Tensor], bias_up: Optional[torch.Tensor],

@@ -119,9 +119,12 @@ class GatedLinearAttention(Part):
         proj, c0 = (self.proj(ctx, x, "gla_proj"), 0) if proj is None else proj      # or columns of a wider product
         y = ctx.buffers.take("gla_y", N, (self.Cv,), ctx.dtype)
         raw = ctx.buffers.take("gla_raw", N, (self.Cv,), torch.float32)
+        longest = N - ctx.num_seqs + 1                 # no request brings more: a function of the step's shape alone
+        need = ops.gated_linear_attention_seg_scratch(ctx.num_seqs, longest, self.H, self.dk, self.dv)
+        segs = ctx.buffers.take_flat("gla_segments", need, torch.float32) if need else None
         ops.gated_linear_attention(y, proj, (c0, c0 + self.Cqk, c0 + 2 * self.Cqk), self.f_bias, self.lower, self.norm_w,
                                    cache.state("S"), ctx.seq_starts, ctx.seq_rows, self.H, self.dk, self.dv,
-                                   self.eps, scratch=raw)
+                                   self.eps, scratch=raw, longest=longest, seg_scratch=segs)
         return Branch(self.o(ctx, y, self.out_buffer, out="partial"))
 
 

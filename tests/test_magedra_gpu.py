@@ -120,11 +120,13 @@ def test_min_gru_kernel(dtype, W):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("shape", [(2, 12, 20), (1, 70, 9), (3, 130, 8), (2, 5, 7), (4, 48, 64)])
-def test_gated_linear_attention_kernel(dtype, shape):
+@pytest.mark.parametrize("lens", [[45, 3], [300, 40], [1, 1]])
+def test_gated_linear_attention_kernel(dtype, shape, lens):
+    """Two requests, one continued from a state, in one launch; long portions run as segments joined in order."""
     from socrates_b200.kernels import ops
     H, D, Dv = shape
     g = torch.Generator().manual_seed(sum(shape))
-    lens, eps = [45, 3], 1e-5
+    eps = 1e-5
     C = 2 * H * D + H * Dv
     proj = (torch.randn(sum(lens), C, generator=g) * 1.5).to(dtype)
     fb, low = torch.randn(H * D, generator=g) + 1.5, torch.rand(H * D, generator=g) * 0.9
@@ -144,8 +146,12 @@ def test_gated_linear_attention_kernel(dtype, shape):
         at += n
     out = torch.empty(sum(lens), H * Dv, device=DEV, dtype=dtype)
     st = state.to(DEV)
+    need = ops.gated_linear_attention_seg_scratch(2, sum(lens) - 1, H, D, Dv)
+    assert (need > 0) == (sum(lens) > 129)
     ops.gated_linear_attention(out, proj.to(DEV), (0, H * D, 2 * H * D), fb.to(DEV), low.to(DEV), nw.to(DEV), st,
-                               i32([0, 45, 48]), i32([1, 0]), H, D, Dv, eps, torch.empty(sum(lens) * H * Dv, device=DEV))
+                               i32([0, lens[0], sum(lens)]), i32([1, 0]), H, D, Dv, eps,
+                               torch.empty(sum(lens) * H * Dv, device=DEV),
+                               seg_scratch=torch.empty(need, device=DEV) if need else None)
     assert part_err(out.double().cpu(), torch.stack(want)) < (1e-5 if dtype == torch.float32 else 2e-2)
     assert part_err(st[0].double().cpu(), S) < 1e-5 and torch.equal(st[2].cpu(), state[2])
 
