@@ -26,7 +26,7 @@ using namespace sb;
 
 namespace {
 
-constexpr int THREADS = 128;
+constexpr int THREADS = 256;    // two threads a key (and a value dim): each takes every other group of rows
 constexpr int KEYS = 128;
 constexpr int RGRP = 4;        // rows whose dot products a thread forms side by side
 constexpr int VG = 16;         // value rows a thread holds at a time
@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
     float* rescale = run_sum + ROWS;
     int* pg = reinterpret_cast<int*>(rescale + ROWS);  // [KEYS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kt = tid & (KEYS - 1), part = tid / KEYS;     // the key (value dim) of this thread, and which half of the rows
     for (int i = tid; i < H * H; i += THREADS) talk_s[i] = a.talk[i];     // weights: before the wait
     sb::pdl_wait();
     // tiles are served last first: a request's late tiles see the most keys and should not start last
@@ -106,14 +107,14 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
 
     for (int c0 = lo; c0 < hi; c0 += KEYS) {
         const int nk = min(KEYS, hi - c0);
-        const int key = c0 + tid;
-        const bool have = tid < nk;
+        const int key = c0 + kt;
+        const bool have = kt < nk;
         // ---- raw scores of this thread's key against every row
         int page = 0;
-        if (have) { page = table[key / BS]; pg[tid] = page; }
+        if (have) { page = table[key / BS]; pg[kt] = page; }
         for (int kh = 0; kh < Hkv; ++kh) {
             const T* kr = kp + (((size_t)page * Hkv + kh) * BS + key % BS) * Dk;
-            for (int r0 = 0; r0 < RK; r0 += RGRP) {
+            for (int r0 = part * RGRP; r0 < RK; r0 += 2 * RGRP) {
                 const int rn = min(RGRP, RK - r0);
                 const float* qrow = Qs + (size_t)(kh * RK + r0) * DkP;
                 float dot[RGRP];
@@ -154,12 +155,12 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
                 }
 #pragma unroll
                 for (int j = 0; j < RGRP; ++j)
-                    if (j < rn) Praw[(size_t)(kh * RK + r0 + j) * KEYS + tid] = dot[j];
+                    if (j < rn) Praw[(size_t)(kh * RK + r0 + j) * KEYS + kt] = dot[j];
             }
         }
-        // ---- every head's score from all heads' raw scores of the same (query, key); mask; scale.
-        // (a thread reads only what it wrote itself: no barrier in between)
-        for (int qi = 0; qi < QT; ++qi) {
+        __syncthreads();
+        // ---- every head's score from all heads' raw scores of the same (query, key); mask; scale
+        for (int qi = part; qi < QT; qi += 2) {
             const int pos = pos_first + qi;
             const int lo_q = (a.window > 0 && pos + 1 > a.window) ? pos + 1 - a.window : 0;
             const bool seen = have && qi < nq && key <= pos && key >= lo_q;
@@ -170,10 +171,10 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
                     const float* tw = talk_s + h * H;
                     for (int kh = 0; kh < Hkv; ++kh)
                         for (int g = 0; g < G; ++g)
-                            s = fmaf(tw[kh * G + g], Praw[(size_t)(kh * RK + qi * G + g) * KEYS + tid], s);
+                            s = fmaf(tw[kh * G + g], Praw[(size_t)(kh * RK + qi * G + g) * KEYS + kt], s);
                     s *= a.scale;
                 }
-                Pmix[(size_t)((h / G) * RK + qi * G + h % G) * KEYS + tid] = s;
+                Pmix[(size_t)((h / G) * RK + qi * G + h % G) * KEYS + kt] = s;
             }
         }
         __syncthreads();
@@ -201,8 +202,8 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
         }
         __syncthreads();
         // ---- weighted values: this thread's value dim; sixteen value rows of a KV head at a time
-        for (int d0 = 0; d0 < Dv; d0 += THREADS) {
-            const int dim = d0 + tid;
+        for (int d0 = 0; d0 < Dv; d0 += KEYS) {
+            const int dim = d0 + kt;
             if (dim >= Dv) continue;
             for (int kh = 0; kh < Hkv; ++kh) {
                 for (int t0 = 0; t0 < nk; t0 += VG) {
@@ -212,7 +213,7 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
                         const int t = t0 + j;
                         v[j] = t < nk ? to_float(vp[(((size_t)pg[t] * Hkv + kh) * BS + (c0 + t) % BS) * Dv + dim]) : 0.f;
                     }
-                    for (int rr = 0; rr < RK; ++rr) {
+                    for (int rr = part; rr < RK; rr += 2) {
                         const int row = kh * RK + rr;
                         float acc = Acc[(size_t)row * Dv + dim];
                         if (t0 == 0) acc *= rescale[row];
