@@ -122,11 +122,15 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
                 for (int j = 0; j < RGRP; ++j) dot[j] = 0.f;
                 if (have) {
                     if (vec_keys) {
-                        for (int d0 = 0; d0 < Dk; d0 += 4 * VEC) {          // four 16-byte pieces in flight
-                            Vec16<T> kv[4];
+                        // four 16-byte pieces at a time, the next four on their way while these are used
+                        Vec16<T> kv[4], nx[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            if (u * VEC < Dk) kv[u].load(kr + u * VEC);
+                        for (int d0 = 0; d0 < Dk; d0 += 4 * VEC) {
 #pragma unroll
                             for (int u = 0; u < 4; ++u)
-                                if (d0 + u * VEC < Dk) kv[u].load(kr + d0 + u * VEC);
+                                if (d0 + (4 + u) * VEC < Dk) nx[u].load(kr + d0 + (4 + u) * VEC);
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {
                                 const int d = d0 + u * VEC;
@@ -143,6 +147,8 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
                                     }
                                 }
                             }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) kv[u] = nx[u];
                         }
                     } else {
                         for (int d = 0; d < Dk; ++d) {
@@ -206,13 +212,18 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
             const int dim = d0 + kt;
             if (dim >= Dv) continue;
             for (int kh = 0; kh < Hkv; ++kh) {
-                for (int t0 = 0; t0 < nk; t0 += VG) {
-                    float v[VG];
+                // sixteen value rows at a time, the next sixteen on their way while these are added
+                float v[VG], vn[VG];
+                auto fetch = [&](float* dst, int t0) {
 #pragma unroll
                     for (int j = 0; j < VG; ++j) {
                         const int t = t0 + j;
-                        v[j] = t < nk ? to_float(vp[(((size_t)pg[t] * Hkv + kh) * BS + (c0 + t) % BS) * Dv + dim]) : 0.f;
+                        dst[j] = t < nk ? to_float(vp[(((size_t)pg[t] * Hkv + kh) * BS + (c0 + t) % BS) * Dv + dim]) : 0.f;
                     }
+                };
+                fetch(v, 0);
+                for (int t0 = 0; t0 < nk; t0 += VG) {
+                    if (t0 + VG < nk) fetch(vn, t0 + VG);
                     for (int rr = part; rr < RK; rr += 2) {
                         const int row = kh * RK + rr;
                         float acc = Acc[(size_t)row * Dv + dim];
@@ -225,6 +236,8 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
                         }
                         Acc[(size_t)row * Dv + dim] = acc;
                     }
+#pragma unroll
+                    for (int j = 0; j < VG; ++j) v[j] = vn[j];
                 }
             }
         }

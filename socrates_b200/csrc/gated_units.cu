@@ -137,6 +137,7 @@ __global__ void __launch_bounds__(128) head_matmul_kernel(HeadArgs a) {
         }
         __syncthreads();
         if (o < nout) {
+#pragma unroll 8
             for (int d = 0; d < ni; ++d) {
                 const float wv = a.transposed ? to_float(w[(size_t)(i0 + d) * a.B + o]) : to_float(w[(size_t)o * a.B + i0 + d]);
 #pragma unroll
