@@ -112,9 +112,12 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
         // ---- raw scores of this thread's key against every row
         int page = 0;
         if (have) { page = table[key / BS]; pg[kt] = page; }
-        for (int kh = 0; kh < Hkv; ++kh) {
+        // (KV head, group of four rows) pairs are dealt to the two threads of a key in turn
+        const int groups = (RK + RGRP - 1) / RGRP;
+        for (int unit = part; unit < Hkv * groups; unit += THREADS / KEYS) {
+            const int kh = unit / groups, r0 = (unit - kh * groups) * RGRP;
             const T* kr = kp + (((size_t)page * Hkv + kh) * BS + key % BS) * Dk;
-            for (int r0 = part * RGRP; r0 < RK; r0 += 2 * RGRP) {
+            {
                 const int rn = min(RGRP, RK - r0);
                 const float* qrow = Qs + (size_t)(kh * RK + r0) * DkP;
                 float dot[RGRP];
@@ -166,11 +169,12 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
         }
         __syncthreads();
         // ---- every head's score from all heads' raw scores of the same (query, key); mask; scale
-        for (int qi = part; qi < QT; qi += 2) {
+        for (int unit = part; unit < QT * H; unit += THREADS / KEYS) {
+            const int qi = unit / H, h = unit - qi * H;
             const int pos = pos_first + qi;
             const int lo_q = (a.window > 0 && pos + 1 > a.window) ? pos + 1 - a.window : 0;
             const bool seen = have && qi < nq && key <= pos && key >= lo_q;
-            for (int h = 0; h < H; ++h) {
+            {
                 float s = -INFINITY;
                 if (seen) {
                     s = 0.f;
@@ -211,7 +215,10 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
         for (int d0 = 0; d0 < Dv; d0 += KEYS) {
             const int dim = d0 + kt;
             if (dim >= Dv) continue;
-            for (int kh = 0; kh < Hkv; ++kh) {
+            // the two threads of a value dim share the KV heads when their number is even (each reads its own value
+            // rows), else the rows of every KV head
+            const bool by_head = Hkv % 2 == 0;
+            for (int kh = by_head ? part : 0; kh < Hkv; kh += by_head ? 2 : 1) {
                 // sixteen value rows at a time, the next sixteen on their way while these are added
                 float v[VG], vn[VG];
                 auto fetch = [&](float* dst, int t0) {
@@ -224,7 +231,7 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
                 fetch(v, 0);
                 for (int t0 = 0; t0 < nk; t0 += VG) {
                     if (t0 + VG < nk) fetch(vn, t0 + VG);
-                    for (int rr = part; rr < RK; rr += 2) {
+                    for (int rr = by_head ? 0 : part; rr < RK; rr += by_head ? 1 : 2) {
                         const int row = kh * RK + rr;
                         float acc = Acc[(size_t)row * Dv + dim];
                         if (t0 == 0) acc *= rescale[row];
@@ -279,14 +286,18 @@ int gcd_(int a, int b) { return b == 0 ? a : gcd_(b, a % b); }
 }  // namespace
 
 // Queries of a tile for prompt portions: a multiple of the smallest count that makes the rows of a KV head a
-// multiple of four (the dot products are formed four rows at a time), as many as keep about 48 rows and
-// 100 KB of shared memory (two blocks an SM); one query when even that does not fit.  0: the shape is not served.
+// multiple of four (the dot products are formed four rows at a time); one query when even that does not fit.
+// 0: the shape is not served.
 extern "C" int sb_attention_talk_tile(int H, int Hkv, int Dk, int Dv) {
     if (H < 1 || Hkv < 1 || H % Hkv || Dk < 1 || Dv < 1) return 0;
     const int G = H / Hkv, unit = RGRP / gcd_(G, RGRP);
-    int QT = unit * (48 / (H * unit) > 0 ? 48 / (H * unit) : 1);
-    while (QT > unit && talk_smem(QT, H, Dk, Dv) > 100 * 1024) QT -= unit;
-    if (talk_smem(QT, H, Dk, Dv) > 100 * 1024) QT = 1;
+    // few heads: about 48 rows and 100 KB, two blocks an SM; many heads: up to 96 rows and 200 KB in one block, so
+    // that several queries still share every key and value row
+    const int rows = H <= 24 ? 48 : 96;
+    const size_t room = H <= 24 ? 100 * 1024 : 200 * 1024;
+    int QT = unit * (rows / (H * unit) > 0 ? rows / (H * unit) : 1);
+    while (QT > unit && talk_smem(QT, H, Dk, Dv) > room) QT -= unit;
+    if (talk_smem(QT, H, Dk, Dv) > room) QT = 1;
     return talk_smem(QT, H, Dk, Dv) <= 220 * 1024 ? QT : 0;
 }
 
