@@ -456,8 +456,9 @@ def _magedra(width, heads):
     """A Magedra configuration at real layer widths, eight layer runs over four layers' weights: a minGRU of the
     model's width; attention with mixed scores (heads of 128 dims, a quarter as many KV heads, half of the dims
     rotating, gated) beside a gated linear attention of half as many heads with key rows of 64 and values of 128;
-    latent attention with heads of 128 + 64 dims over a latent of 128; a minGRU again; four residual streams;
-    clamped gated feed-forwards of four times the width."""
+    latent attention with heads of 128 + 32 dims over a latent of 96 (a cached row of 32 + 96 = 128 dims, which the
+    bfloat16 engine's prompt portions read on the tensor cores); a minGRU again; four residual streams; clamped gated
+    feed-forwards of four times the width."""
     ff = {"kind": "dense", "ff": 4 * width, "limit": 7.0}
     gru = {"type": "mingru", "mixer": {"width": width}, "mlp": dict(ff)}
     par = {"type": "parallel", "mlp": dict(ff), "mixer": {
@@ -465,8 +466,8 @@ def _magedra(width, heads):
                  "rot": {"dims": 64, "base": 1e6}},
         "right": {"heads": max(1, heads // 2), "dim": 64, "vdim": 128}, "left_scale": 1.0, "right_scale": 1.0}}
     lat = {"type": "latent_attention", "mlp": dict(ff), "mixer": {
-        "heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": width // 2, "kv_rank": 128,
-        "scale": 192 ** -0.5, "rot": {"base": 1e4, "dims": 64}}}
+        "heads": heads, "dim": 128, "rot_dim": 32, "vdim": 128, "q_rank": width // 2, "kv_rank": 96,
+        "scale": 160 ** -0.5, "rot": {"base": 1e4, "dims": 32}}}
     four = [gru, par, lat, dict(gru, mixer=dict(gru["mixer"]))]
     again = [dict(l, weights_of=i) for i, l in enumerate(four)]
     return {"architecture": "Magedra", "vocab": 32000, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,

@@ -13,7 +13,9 @@ kv_rank` dims with c again as its value, the engine's paged attention runs `head
 head, and its output (sum_j p c_j per head) goes through W_uv,h afterwards.  The rows of W_uq are reordered
 when the weights are bound so that every head's turning part comes first.  One kernel norms the latent, turns
 the key part and the queries and writes the token's row into its pages.
-Norms, angles, scores, weights and sums are float32; the per-head matrices accumulate in float32.
+Norms, angles, scores, weights and sums are float32; the per-head matrices accumulate in float32.  One exception, in
+the bfloat16 engine only: prompt portions of layers whose cached row has 64 or 128 dims run on the tensor-core tile
+kernel (the key rows serve as values too), where each softmax weight enters the value product as two bfloat16 terms.
 Tensors: `<name>dq`, `dq.norm`, `uq`, `dkv`, `dkv.norm`, `uk`, `uv`, `o`.
 """
 
@@ -98,20 +100,33 @@ class LatentAttention(Part):
         ops.latent_write(down, self.q_rank, self.q_rank + rank, rank, rotary_dim, self.kv_gain, self.eps, q, H,
                          inv_freq, self.position.neighbours, getattr(self.position, "magnitude", 1.0),
                          ctx.positions, ctx.token_rows, table, k_pool, v_pool)
-        lat = ctx.buffers.take("la_lat", N, (H * rank,), ctx.dtype)
-        if (not ctx.all_decode and N >= 4 * ctx.num_seqs
+        src, first, step = None, 0, rank                   # where the attention output lies: matrix, first column, head stride
+        if (not ctx.all_decode and ctx.dtype == torch.bfloat16 and ctx.status is not None and D in (64, 128)
+                and ops.attention_tcgen05_supports(H, 1, D, k_pool.shape[2])):
+            # prompt portions in the bfloat16 engine whose cached row has 64 or 128 dims: the tensor-core tile kernel,
+            # with the key rows [k_rot | c] as the values too, so that keys and values have one size; the head's
+            # output is then sum_j p [k_rot | c]_j, of which only the latent part is carried on.  Scores are float32
+            # sums over the bfloat16 q and k, softmax is float32, each weight enters the value product as two
+            # bfloat16 terms.
+            src = ctx.buffers.take("la_wide", N, (H * D,), ctx.dtype)
+            ops.attention_prefill_tcgen05(src, q, k_pool, k_pool, table, ctx.seq_starts, ctx.seq_rows, ctx.seq_first_pos,
+                                          H, self.scale, ctx.status, self.window or 0)
+            first, step = dr, D
+        elif (not ctx.all_decode and N >= 4 * ctx.num_seqs
                 and ops.attention_bias_tile_supports(H, 1, D, rank, ctx.dtype)):
-            ops.attention_bias_tile(lat, q, k_pool, v_pool, table, ctx.seq_starts, ctx.seq_rows, ctx.seq_first_pos,
+            src = ctx.buffers.take("la_lat", N, (H * rank,), ctx.dtype)
+            ops.attention_bias_tile(src, q, k_pool, v_pool, table, ctx.seq_starts, ctx.seq_rows, ctx.seq_first_pos,
                                     H, self.scale, self.window or 0)
         else:
+            src = ctx.buffers.take("la_lat", N, (H * rank,), ctx.dtype)
             NP, part_o, part_ml = self.partitions(ctx, N, cache.manager.max_len), None, None
             if NP > 1:
                 part_o = ctx.buffers.take_flat("attn_part_o", N * H * NP * rank, torch.float32)
                 part_ml = ctx.buffers.take_flat("attn_part_ml", N * H * NP * 2, torch.float32)
-            ops.attention_bias(lat, q, k_pool, v_pool, table, ctx.token_rows, ctx.positions, H, self.scale,
+            ops.attention_bias(src, q, k_pool, v_pool, table, ctx.token_rows, ctx.positions, H, self.scale,
                                self.window or 0, num_partitions=NP, part_o=part_o, part_ml=part_ml)
         heads = ctx.buffers.take("la_heads", N, (H * self.dv,), ctx.dtype)
-        ops.head_matmul(heads, 0, self.dv, lat, 0, rank, self.uv, H, transposed=False)
+        ops.head_matmul(heads, 0, self.dv, src, first, step, self.uv, H, transposed=False)
         return Branch(self.o(ctx, heads, self.out_buffer, out="partial"))
 
 

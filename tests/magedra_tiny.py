@@ -4,7 +4,8 @@ The configurations differ from one another in every size and option: 1, 2, 3 and
 at all, branch factors above, below and equal to one, a logit scale and none; attention with 1, 2 and 4 query
 heads per key/value head, key rows of 6 to 64 dims (multiples of the 16-byte vector and not), values smaller
 and larger than a key row and beyond 128 dims, full, partial and no rotation; linear attention with key rows
-that need 4, 8 and 16 state rows a thread; latents smaller and larger than 128 dims; recurrences narrower and
+that need 4, 8 and 16 state rows a thread; latents smaller and larger than 128 dims, and cached rows of exactly 64 and
+128 dims (which the bfloat16 engine serves on the tensor cores); recurrences narrower and
 wider than a block of 128 channels; layers with and without a feed-forward; layers that run an earlier
 layer's weights (next to it and further on); and one model whose sizes are no multiple of 8.
 """
@@ -46,7 +47,7 @@ def _layer(kind, mixer, mlp, weights_of=None):
 
 _G0, _P0, _L0 = _gru(24), _par(4, 2, 16, 8, 0.3, 2, 12, 20, rot=8, base=100.0, ls=1.3, rs=0.8), _lat(3, 8, 4, 12, 16, 20, 0.35, 1000.0)
 _P2 = _par(2, 1, 64, 32, 0.12, 3, 130, 8, rot=64, base=50000.0, ls=0.7, rs=1.1)
-_L2 = _lat(4, 16, 8, 16, 24, 32, 0.2, 20000.0)
+_L2 = _lat(4, 16, 8, 16, 24, 56, 0.2, 20000.0)      # a cached row of 8 + 56 = 64 dims
 
 TINY = {
     # three streams; every mixer; layers run again next to their owner and later; a layer without a feed-forward
@@ -79,7 +80,8 @@ TINY = {
     "E": {"architecture": "Magedra", "vocab": 80, "width": 56, "norm": {"eps": 1e-6}, "residual_mult": 0.4, "streams": 8,
           "logit_scale": 2.0,
           "layers": [_layer("parallel", _par(8, 2, 32, 64, 0.18, 2, 32, 16, rot=16, base=1000.0, ls=1.0, rs=1.0), _dense(64, 2.5)),
-                     _layer("mingru", _gru(40), _dense(64, 2.5))]},
+                     _layer("mingru", _gru(40), _dense(64, 2.5)),
+                     _layer("latent_attention", _lat(8, 32, 32, 64, 48, 96, 0.12, 5000.0), _dense(64, 2.5))]},   # a row of 128
 }
 
 

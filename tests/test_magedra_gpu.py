@@ -163,19 +163,20 @@ def test_small_steps(dtype):
     from socrates_b200.kernels import ops
     g = torch.Generator().manual_seed(1)
     tol = 1e-5 if dtype == torch.float32 else 1e-2
-    N, F_ = 13, 21
-    x = (torch.randn(N, 2 * F_, generator=g) * 2).to(dtype)
-    bg, bu = torch.randn(F_, generator=g), torch.randn(F_, generator=g)
-    for lim in (0.5, 2.0):
-        gg = (x.double()[:, :F_] + bg.double()).clamp(max=lim)
-        uu = (x.double()[:, F_:] + bu.double()).clamp(-lim, lim)
-        want = gg * plain.sigmoid(1.702 * gg) * (uu + 1.0)
-        out = torch.empty(N, F_, device=DEV, dtype=dtype)
-        ops.glu_clamp(out, x.to(DEV), bg.to(DEV), bu.to(DEV), lim, 1.702, 1.0)
-        assert part_err(out.double().cpu(), want) < tol
-        parts = torch.stack([x.float() * 0.25, x.float() * 0.75]).to(DEV)
-        ops.glu_clamp(out, parts, bg.to(DEV), bu.to(DEV), lim, 1.702, 1.0)
-        assert part_err(out.double().cpu(), want) < tol
+    for N, F_ in ((13, 21), (9, 24), (300, 64)):           # rows of single values, and of whole 16-byte pieces
+        x = (torch.randn(N, 2 * F_, generator=g) * 2).to(dtype)
+        bg, bu = torch.randn(F_, generator=g), torch.randn(F_, generator=g)
+        for lim in (0.5, 2.0):
+            gg = (x.double()[:, :F_] + bg.double()).clamp(max=lim)
+            uu = (x.double()[:, F_:] + bu.double()).clamp(-lim, lim)
+            want = gg * plain.sigmoid(1.702 * gg) * (uu + 1.0)
+            out = torch.empty(N, F_, device=DEV, dtype=dtype)
+            ops.glu_clamp(out, x.to(DEV), bg.to(DEV), bu.to(DEV), lim, 1.702, 1.0)
+            assert part_err(out.double().cpu(), want) < tol
+            parts = torch.stack([x.float() * 0.25, x.float() * 0.75]).to(DEV)
+            ops.glu_clamp(out, parts, bg.to(DEV), bu.to(DEV), lim, 1.702, 1.0)
+            assert part_err(out.double().cpu(), want) < tol
+    N = 13
     # segments
     x = torch.randn(N, 50, generator=g).to(dtype)
     g1, g2 = torch.rand(17, generator=g) + 0.5, torch.rand(20, generator=g) + 0.5
@@ -309,7 +310,7 @@ def plain_mixer(kind, x, w, pre, m, eps):
 def test_mixers_alone(tmp_path, dtype):
     g = torch.Generator().manual_seed(4)
     for name, layer, entry in (("A", 0, 0), ("A", 0, 4), ("A", 1, 1), ("A", 1, 2), ("A", 2, 3), ("B", 0, 0), ("B", 1, 1),
-                               ("B", 2, 2), ("C", 0, 2), ("C", 1, 1), ("D", 0, 3), ("D", 1, 1), ("D", 2, 2), ("E", 0, 0)):
+                               ("B", 2, 2), ("C", 0, 2), ("C", 1, 1), ("D", 0, 3), ("D", 1, 1), ("D", 2, 2), ("E", 0, 0), ("E", 2, 2)):
         folder, cfg, w = make_folder(tmp_path, name)
         spec = [l for l in cfg["layers"] if "weights_of" not in l][layer]
         pre = "l%d.mix." % cfg["layers"].index(spec)
