@@ -276,6 +276,134 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
     }
 }
 
+// ----------------------------------------------------------------------------------------
+// The same attention for ONE long prompt portion in the bfloat16 engine, with both products on the tensor
+// cores through the engine's matrix product: the portion's keys are gathered out of their pages into one
+// matrix per KV head (values transposed, twice side by side), the raw scores of a block of queries are one
+// product per KV head (float32 sums over the bfloat16 q and k), a kernel mixes them across the heads, masks,
+// takes the softmax in float32 and writes every weight as two bfloat16 terms [high | low], and the weighted
+// values are one more product per KV head over both terms.  The kernels here are the three steps between
+// the products.
+struct TalkDenseArgs {
+    const __nv_bfloat16* q;        // [N, H*Dk]
+    const __nv_bfloat16* k_pool;   // [pages, Hkv, BS, Dk]
+    const __nv_bfloat16* v_pool;   // [pages, Hkv, BS, Dv]
+    const int* table;              // the request's row of the block table
+    __nv_bfloat16* Kc;             // [Hkv, Cp, Dk]
+    __nv_bfloat16* Vt;             // [Hkv, Dv, 2*Cp]
+    __nv_bfloat16* Qg;             // [Hkv, G*nb, Dk]
+    const float* S;                // [Hkv, G*nb, Cp] raw scores
+    __nv_bfloat16* P;              // [Hkv, G*nb, 2*Cp] weights, high and low terms
+    const float* O;                // [Hkv, G*nb, Dv]
+    __nv_bfloat16* out;            // [N, H*Dv]
+    const __nv_bfloat16* gate;     // [N, gate_stride] or null
+    long long gate_stride;
+    const float* talk;             // [H, H]
+    int H, Hkv, Dk, Dv, BS, C, Cp, n0, nb, pos0, window;     // C keys; queries n0 .. n0+nb-1 at positions pos0 ..
+    float scale;
+};
+
+// keys of 64 positions of one KV head: rows into Kc, value rows transposed into both halves of Vt
+__global__ void __launch_bounds__(256) talk_gather_kv_kernel(TalkDenseArgs a) {
+    sb::pdl_launch_dependents();
+    extern __shared__ __nv_bfloat16 vt[];       // [64][Dv + 2]
+    const int j0 = blockIdx.x * 64, kh = blockIdx.y, Dk = a.Dk, Dv = a.Dv, P2 = Dv + 2;
+    sb::pdl_wait();
+    for (int i = threadIdx.x; i < 64 * Dk; i += blockDim.x) {
+        const int jj = i / Dk, d = i - jj * Dk, j = j0 + jj;
+        __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+        if (j < a.C) v = a.k_pool[(((size_t)a.table[j / a.BS] * a.Hkv + kh) * a.BS + j % a.BS) * Dk + d];
+        a.Kc[((size_t)kh * a.Cp + j) * Dk + d] = v;
+    }
+    for (int i = threadIdx.x; i < 64 * Dv; i += blockDim.x) {
+        const int jj = i / Dv, e = i - jj * Dv, j = j0 + jj;
+        __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+        if (j < a.C) v = a.v_pool[(((size_t)a.table[j / a.BS] * a.Hkv + kh) * a.BS + j % a.BS) * Dv + e];
+        vt[jj * P2 + e] = v;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * Dv; i += blockDim.x) {
+        const int e = i / 64, jj = i - e * 64;
+        const __nv_bfloat16 v = vt[jj * P2 + e];
+        __nv_bfloat16* row = a.Vt + ((size_t)kh * Dv + e) * 2 * a.Cp;
+        row[j0 + jj] = v;
+        row[a.Cp + j0 + jj] = v;
+    }
+}
+
+// queries of the block, the heads of a KV head one under the other
+__global__ void __launch_bounds__(256) talk_gather_q_kernel(TalkDenseArgs a) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    const int i = blockIdx.x, G = a.H / a.Hkv;
+    for (int c = threadIdx.x; c < a.H * a.Dk; c += blockDim.x) {
+        const int h = c / a.Dk, d = c - h * a.Dk, kh = h / G, g = h - kh * G;
+        a.Qg[((size_t)kh * G * a.nb + (size_t)g * a.nb + i) * a.Dk + d] = a.q[(size_t)(a.n0 + i) * a.H * a.Dk + c];
+    }
+}
+
+// one (query, head): mix the raw scores of all heads, mask, softmax, two bfloat16 terms a weight
+__global__ void __launch_bounds__(256) talk_mix_softmax_kernel(TalkDenseArgs a) {
+    sb::pdl_launch_dependents();
+    extern __shared__ float row[];              // Cp mixed scores
+    __shared__ float scratch[33], tw[64];
+    const int i = blockIdx.x, h = blockIdx.y, H = a.H, G = H / a.Hkv, Cp = a.Cp;
+    for (int g = threadIdx.x; g < H; g += blockDim.x) tw[g] = a.talk[h * H + g] * a.scale;
+    sb::pdl_wait();
+    __syncthreads();
+    const int pos = a.pos0 + i;
+    const int lo = (a.window > 0 && pos + 1 > a.window) ? pos + 1 - a.window : 0;
+    const int hi = min(pos, a.C - 1);           // keys lo .. hi are seen
+    float mx = -INFINITY;
+    for (int j = lo + threadIdx.x; j <= hi; j += blockDim.x) {
+        float s = 0.f;
+        for (int g = 0; g < H; ++g) {
+            const int kh = g / G, gg = g - kh * G;
+            s = fmaf(tw[g], a.S[((size_t)kh * G * a.nb + (size_t)gg * a.nb + i) * Cp + j], s);
+        }
+        row[j] = s;
+        mx = fmaxf(mx, s);
+    }
+    // block maximum (block_sum's scratch, the same order every time)
+    mx = warp_max(mx);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = -INFINITY;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, scratch[w]);
+    float sum = 0.f;
+    for (int j = lo + threadIdx.x; j <= hi; j += blockDim.x) {
+        const float p = expf(row[j] - mx);
+        row[j] = p;
+        sum += p;
+    }
+    const float inv = 1.0f / block_sum(sum, scratch);
+    const int kh = h / G, gg = h - kh * G;
+    __nv_bfloat16* pr = a.P + ((size_t)kh * G * a.nb + (size_t)gg * a.nb + i) * 2 * Cp;
+    for (int j = threadIdx.x; j < Cp; j += blockDim.x) {
+        float p = (j >= lo && j <= hi) ? row[j] * inv : 0.f;
+        const __nv_bfloat16 ph = __float2bfloat16_rn(p);
+        pr[j] = ph;
+        pr[Cp + j] = __float2bfloat16_rn(p - __bfloat162float(ph));
+    }
+}
+
+// the heads' outputs back in their places, gated
+__global__ void __launch_bounds__(256) talk_finish_kernel(TalkDenseArgs a) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    const int i = blockIdx.x, G = a.H / a.Hkv, n = a.n0 + i;
+    for (int c = threadIdx.x; c < a.H * a.Dv; c += blockDim.x) {
+        const int h = c / a.Dv, e = c - h * a.Dv, kh = h / G, g = h - kh * G;
+        float o = a.O[((size_t)kh * G * a.nb + (size_t)g * a.nb + i) * a.Dv + e];
+        if (a.gate) {
+            const float z = __bfloat162float(a.gate[(size_t)n * a.gate_stride + c]);
+            o *= 1.0f / (1.0f + expf(-z));
+        }
+        a.out[(size_t)n * a.H * a.Dv + c] = __float2bfloat16_rn(o);
+    }
+}
+
 size_t talk_smem(int QT, int H, int Dk, int Dv) {
     const size_t rows = (size_t)QT * H, dkp = (Dk + 3) & ~3;
     return (rows * (dkp + 2 * KEYS + Dv + 3) + (size_t)H * H + KEYS) * sizeof(float);
@@ -347,6 +475,44 @@ extern "C" int sb_attention_talk(void* out, const void* q, const void* k_pool, c
                        (const float*)part_o, (const float*)part_ml, H, Dv, num_partitions);
     } else {
         SB_REQUIRE(false, "attention_talk: unknown dtype %d", dtype);
+    }
+    SB_LAUNCH_CHECK();
+}
+
+// Steps of the tensor-core form for one long prompt portion (see TalkDenseArgs).  step 0: gather keys and values of
+// the request's C keys; 1: gather the block's queries; 2: mix, mask and softmax the block's raw scores; 3: write
+// the block's outputs.  All matrices are the caller's; Cp = C rounded up to a multiple of 64.
+extern "C" int sb_attention_talk_dense(int step, const void* q, const void* k_pool, const void* v_pool, const int* table,
+                                       void* Kc, void* Vt, void* Qg, const float* S, void* P, const float* O, void* out,
+                                       const void* gate, long long gate_stride, const float* talk, int H, int Hkv, int Dk,
+                                       int Dv, int page_size, int C, int Cp, int n0, int nb, int pos0, int window,
+                                       float scale, cudaStream_t stream) {
+    SB_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0 && H <= 64, "attention_talk_dense: %d heads over %d KV heads (at most 64)", H, Hkv);
+    SB_REQUIRE(C > 0 && Cp >= C && Cp % 64 == 0 && nb > 0 && step >= 0 && step <= 3, "attention_talk_dense: bad sizes");
+    SB_REQUIRE(nb <= 65535 && Cp / 64 <= 65535, "attention_talk_dense: a block of %d queries over %d keys exceeds one launch", nb, Cp);
+    TalkDenseArgs a;
+    a.q = (const __nv_bfloat16*)q; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
+    a.table = table; a.Kc = (__nv_bfloat16*)Kc; a.Vt = (__nv_bfloat16*)Vt; a.Qg = (__nv_bfloat16*)Qg; a.S = S;
+    a.P = (__nv_bfloat16*)P; a.O = O; a.out = (__nv_bfloat16*)out; a.gate = (const __nv_bfloat16*)gate;
+    a.gate_stride = gate_stride; a.talk = talk; a.H = H; a.Hkv = Hkv; a.Dk = Dk; a.Dv = Dv; a.BS = page_size; a.C = C;
+    a.Cp = Cp; a.n0 = n0; a.nb = nb; a.pos0 = pos0; a.window = window; a.scale = scale;
+    if (step == 0) {
+        const size_t smem = (size_t)64 * (Dv + 2) * sizeof(__nv_bfloat16);
+        SB_REQUIRE(smem <= 48 * 1024, "attention_talk_dense: value heads of %d dims", Dv);
+        sb::launch(talk_gather_kv_kernel, dim3(Cp / 64, Hkv), dim3(256), smem, stream, a);
+    } else if (step == 1) {
+        sb::launch(talk_gather_q_kernel, dim3(nb), dim3(256), 0, stream, a);
+    } else if (step == 2) {
+        const size_t smem = (size_t)Cp * sizeof(float);
+        SB_REQUIRE(smem <= 200 * 1024, "attention_talk_dense: %d keys do not fit a block's shared memory", Cp);
+        static sb::OncePerDevice once;
+        if (!once.flag()) {
+            cudaFuncSetAttribute(talk_mix_softmax_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            once.flag() = true;
+        }
+        sb::launch(talk_mix_softmax_kernel, dim3(nb, H), dim3(256), smem, stream, a);
+    } else {
+        sb::launch(talk_finish_kernel, dim3(nb), dim3(256), 0, stream, a);
     }
     SB_LAUNCH_CHECK();
 }

@@ -81,6 +81,7 @@ _SIGNATURES = {
     "sb_head_matmul": [P, LL, I, I, P, LL, I, I, P, I, I, I, I, I, I, I, P],
     "sb_latent_write": [P, LL, I, I, I, I, P, F, P, I, P, I, F, P, P, P, I, I, P, P, I, I, P],
     "sb_attention_talk_tile": [I, I, I, I],
+    "sb_attention_talk_dense": [I, P, P, P, P, P, P, P, P, P, P, P, P, LL, P, I, I, I, I, I, I, I, I, I, I, I, F, P],
     "sb_attention_talk": [P, P, P, P, P, I, P, P, P, I, P, P, LL, I, I, I, I, I, I, I, F, I, I, P, P, I, P],
     "sb_attention_bias": [P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P, P, I, I, I, F, P],
 }

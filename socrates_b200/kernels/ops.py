@@ -1369,3 +1369,30 @@ def attention_talk(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_p
                                      float(scale), int(queries_per_tile), int(num_partitions), _ptr(part_o),
                                      _ptr(part_ml), _code(q.dtype), _stream()), "attention_talk",
           kernels=2 if num_partitions > 1 else 1)
+
+
+def attention_talk_dense_step(step: int, q, k_pool, v_pool, table_row, Kc, Vt, Qg, S, P, O, out, gate, talk,
+                              num_heads: int, C: int, Cp: int, n0: int, nb: int, pos0: int, window: int, scale: float) -> None:
+    """One of the steps between the matrix products of the tensor-core form of `attention_talk` for one long prompt
+    portion (bfloat16): 0 gathers the request's C keys and values out of their pages (Kc [Hkv, Cp, Dk]; Vt [Hkv, Dv,
+    2*Cp], the transposed values twice side by side); 1 gathers the queries n0 .. n0+nb-1 (Qg [Hkv, G*nb, Dk]); 2
+    mixes the raw scores S [Hkv, G*nb, Cp] across the heads, masks, takes the softmax in float32 and writes P [Hkv,
+    G*nb, 2*Cp], every weight as a high and a low bfloat16 term; 3 writes O [Hkv, G*nb, Dv] to out [N, H*Dv], gated."""
+    pages, Hkv, BS, Dk = k_pool.shape
+    Dv = v_pool.shape[3]
+    for t in (q, k_pool, v_pool, Kc, Vt, Qg, P, out):
+        _want(t, "a matrix of the dense form", torch.bfloat16)
+    for t in (S, O, talk):
+        _want(t, "a float32 matrix of the dense form", torch.float32)
+    _want(table_row, "table_row", torch.int32)
+    G = num_heads // Hkv
+    if (Kc.numel() < Hkv * Cp * Dk or Vt.numel() < Hkv * Dv * 2 * Cp or Qg.numel() < num_heads * nb * Dk
+            or S.numel() < num_heads * nb * Cp or P.numel() < num_heads * nb * 2 * Cp or O.numel() < num_heads * nb * Dv):
+        raise KernelError("a matrix of the dense form is too small")
+    gate_stride = _gate_stride(gate, q, q.shape[0], num_heads * Dv)
+    lib = library()
+    check(lib, lib.sb_attention_talk_dense(int(step), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table_row), _ptr(Kc),
+                                           _ptr(Vt), _ptr(Qg), _ptr(S), _ptr(P), _ptr(O), _ptr(out), _ptr(gate),
+                                           gate_stride, _ptr(talk), num_heads, Hkv, Dk, Dv, BS, int(C), int(Cp), int(n0),
+                                           int(nb), int(pos0), int(window), float(scale), _stream()),
+          "attention_talk_dense")

@@ -10,8 +10,12 @@ sigmoid gate on the concatenated heads.
 
 Scores, the mixing, weights and the weighted sum are float32 (`csrc/attention_talk.cu`): a block serves all
 heads of a tile of a request's consecutive tokens, since every head's score reads every head's raw score;
-a decode step gives each token a tile of its own and cuts its keys into shares.  All projections are one
-matrix product.  Tensors: `<name>q`, `k`, `v`, `talk`, `g`, `o`.
+a decode step gives each token a tile of its own and cuts its keys into shares.  One exception, in the bfloat16
+engine only: a step that is ONE long prompt portion runs both products on the tensor cores through the engine's
+matrix product (`dense_form`): keys gathered out of their pages, raw scores of a block of queries as one product
+per KV head (float32 sums over the bfloat16 q and k), mixing, mask and softmax in float32 by a kernel that writes
+every weight as two bfloat16 terms, the weighted values as one more product over both terms.  All projections are
+one matrix product.  Tensors: `<name>q`, `k`, `v`, `talk`, `g`, `o`.
 """
 
 from __future__ import annotations
@@ -80,6 +84,53 @@ class TalkingAttention(Part):
         span = min(self.window or max_len, max_len)
         return max(1, min(32, (2 * ctx.num_sms) // max(1, N), -(-span // 128)))
 
+    DENSE_FROM = 128           # tokens from which a lone prompt portion takes the tensor-core form
+    DENSE_SCORES = 1 << 27     # most raw scores of a block of queries (float32: 512 MB)
+
+    def dense_form(self, ctx, q, gate, attn, k_pool, v_pool, table) -> bool:
+        """The tensor-core form for a step that is one prompt portion of one request; False if the step is not
+        such a step (the caller then runs the tile kernel)."""
+        import os
+        entries = ctx.host_batch
+        N = q.shape[0]
+        if (ctx.dtype != torch.bfloat16 or ctx.status is None or entries is None or len(entries) != 1
+                or N < self.DENSE_FROM or self.dk % 8 or self.dv % 8 or self.H > 64 or self.dv > 256
+                or os.environ.get("SOCRATES_TALK_DENSE", "1") == "0"):
+            return False
+        e = entries[0]
+        start, row = int(e.start), int(e.row)
+        C = start + N
+        Cp = -(-C // 64) * 64
+        if Cp * 4 > 200 * 1024:
+            return False
+        H, Hkv, G, dk, dv = self.H, self.G, self.H // self.G, self.dk, self.dv
+        nb_most = max(64, min(N, self.DENSE_SCORES // (H * Cp)))
+        take = ctx.buffers.take_flat
+        Kc = take("talk_kc", Hkv * Cp * dk, ctx.dtype)
+        Vt = take("talk_vt", Hkv * dv * 2 * Cp, ctx.dtype)
+        Qg = take("talk_qg", H * nb_most * dk, ctx.dtype)
+        S = take("talk_s", H * nb_most * Cp, torch.float32)
+        P = take("talk_p", H * nb_most * 2 * Cp, ctx.dtype)
+        O = take("talk_o", H * nb_most * dv, torch.float32)
+        trow = table[row]
+        args = (q, k_pool, v_pool, trow, Kc, Vt, Qg, S, P, O, attn, gate, self.talk, H)
+        ops.attention_talk_dense_step(0, *args, C, Cp, 0, 1, start, self.window or 0, self.scale)
+        for n0 in range(0, N, nb_most):
+            nb = min(nb_most, N - n0)
+            tail = (C, Cp, n0, nb, start + n0, self.window or 0, self.scale)
+            ops.attention_talk_dense_step(1, *args, *tail)
+            for kh in range(Hkv):
+                ctx.gemm(S[kh * G * nb * Cp:(kh + 1) * G * nb * Cp].view(G * nb, Cp),
+                         Qg[kh * G * nb * dk:(kh + 1) * G * nb * dk].view(G * nb, dk),
+                         Kc[kh * Cp * dk:(kh + 1) * Cp * dk].view(Cp, dk))
+            ops.attention_talk_dense_step(2, *args, *tail)
+            for kh in range(Hkv):
+                ctx.gemm(O[kh * G * nb * dv:(kh + 1) * G * nb * dv].view(G * nb, dv),
+                         P[kh * G * nb * 2 * Cp:(kh + 1) * G * nb * 2 * Cp].view(G * nb, 2 * Cp),
+                         Vt[kh * dv * 2 * Cp:(kh + 1) * dv * 2 * Cp].view(dv, 2 * Cp))
+            ops.attention_talk_dense_step(3, *args, *tail)
+        return True
+
     def forward(self, ctx, x: torch.Tensor, cache, proj=None) -> Branch:
         N = x.shape[0]
         if proj is None:
@@ -106,7 +157,7 @@ class TalkingAttention(Part):
             ops.attention_talk(attn, q, k_pool, v_pool, table, ctx.seq_starts, ctx.seq_rows, ctx.seq_first_pos,
                                self.talk, self.H, self.scale, self.window or 0, gate=gate, queries_per_tile=1,
                                num_partitions=NP, part_o=part_o, part_ml=part_ml)
-        else:
+        elif not self.dense_form(ctx, q, gate, attn, k_pool, v_pool, table):
             ops.attention_talk(attn, q, k_pool, v_pool, table, ctx.seq_starts, ctx.seq_rows, ctx.seq_first_pos,
                                self.talk, self.H, self.scale, self.window or 0, gate=gate)
         return Branch(self.o(ctx, attn, self.out_buffer, out="partial"))
