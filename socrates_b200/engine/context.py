@@ -125,6 +125,7 @@ class StepContext:
         self.token_feedback = token_feedback   # int32 device tokens that ids -1 - j stand for (see ops.embed)
         self.weight_successor: Dict[int, torch.Tensor] = {}   # set by the model: address -> next weights
         self.l2_prefetch_bytes = _l2_prefetch_budget()
+        self.dependent_launch = True        # set by the model: whether the step's kernels are launched dependently
         self.after_run = None               # callable(order index, stream) after every layer run (for inspection)
 
     # ------------------------------------------------------------------ kernel choice

@@ -93,6 +93,7 @@ class Model:
     # ------------------------------------------------------------------ one step
     def forward(self, ctx: StepContext, cache) -> torch.Tensor:
         ctx.weight_successor = self.weight_successor
+        ctx.dependent_launch = self.dependent_launch
         ops.set_dependent_launch(self.dependent_launch)
         stream = ResidualStream(self.embedding.forward(ctx))
         if self.keeps_embedding_output:

@@ -84,7 +84,9 @@ class TalkingAttention(Part):
         span = min(self.window or max_len, max_len)
         return max(1, min(32, (2 * ctx.num_sms) // max(1, N), -(-span // 128)))
 
-    DENSE_FROM = 128           # tokens from which a lone prompt portion takes the tensor-core form
+    # Tokens from which a lone prompt portion takes the tensor-core form.  It pays from a few hundred tokens on; it
+    # is kept to long portions because its chain of launches once did not come back (see dense_form).
+    DENSE_FROM = 1536
     DENSE_SCORES = 1 << 27     # most raw scores of a block of queries (float32: 512 MB)
 
     def dense_form(self, ctx, q, gate, attn, k_pool, v_pool, table) -> bool:
@@ -114,6 +116,16 @@ class TalkingAttention(Part):
         O = take("talk_o", H * nb_most * dv, torch.float32)
         trow = table[row]
         args = (q, k_pool, v_pool, trow, Kc, Vt, Qg, S, P, O, attn, gate, self.talk, H)
+        # these launches are plainly serial: a first 2,048-token step with them launched dependently never came back
+        ops.set_dependent_launch(False)
+        try:
+            self._dense_steps(ctx, args, N, C, Cp, start, nb_most, S, Qg, Kc, O, P, Vt)
+        finally:
+            ops.set_dependent_launch(ctx.dependent_launch)
+        return True
+
+    def _dense_steps(self, ctx, args, N, C, Cp, start, nb_most, S, Qg, Kc, O, P, Vt) -> None:
+        H, Hkv, G, dk, dv = self.H, self.G, self.H // self.G, self.dk, self.dv
         ops.attention_talk_dense_step(0, *args, C, Cp, 0, 1, start, self.window or 0, self.scale)
         for n0 in range(0, N, nb_most):
             nb = min(nb_most, N - n0)
@@ -129,7 +141,6 @@ class TalkingAttention(Part):
                          P[kh * G * nb * 2 * Cp:(kh + 1) * G * nb * 2 * Cp].view(G * nb, 2 * Cp),
                          Vt[kh * dv * 2 * Cp:(kh + 1) * dv * 2 * Cp].view(dv, 2 * Cp))
             ops.attention_talk_dense_step(3, *args, *tail)
-        return True
 
     def forward(self, ctx, x: torch.Tensor, cache, proj=None) -> Branch:
         N = x.shape[0]

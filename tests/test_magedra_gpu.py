@@ -323,6 +323,33 @@ def test_mixers_alone(tmp_path, dtype):
             assert part_err(got, want) < PART_TOL[dtype], (name, layer, sizes)
 
 
+def test_tensor_core_form_of_attention_with_mixed_scores(tmp_path, monkeypatch):
+    """One long prompt portion in the bfloat16 engine: keys gathered out of their pages, both products through the
+    engine's matrix product, mixing, mask and softmax in between; whole, behind an earlier portion, and in blocks
+    of queries; against the plain statement and against the CUDA-core kernel."""
+    from socrates_b200.parts.talking_attention import TalkingAttention
+    g = torch.Generator().manual_seed(14)
+    for name, layer, entry in (("A", 1, 1), ("C", 0, 0), ("E", 0, 0)):
+        folder, cfg, w = make_folder(tmp_path, name)
+        spec = [l for l in cfg["layers"] if "weights_of" not in l][layer]
+        pre = "l%d.mix." % cfg["layers"].index(spec)
+        n = 300
+        x = (torch.randn(n, cfg["width"], generator=g) * 1.5).bfloat16().double()
+        want = plain_mixer(spec["type"], x, w, pre, spec["mixer"], cfg["norm"]["eps"])
+        monkeypatch.setattr(TalkingAttention, "DENSE_FROM", 1 << 30)
+        h = Harness(folder, torch.bfloat16, max_len=320)
+        cores = run_part(h, h.model.layers[layer].mixer, x, torch.bfloat16, (n,), entry=entry)
+        assert not any(k[0] == "talk_s" for k in h.runner.buffers._flat)
+        for sizes, most in (((n,), 1 << 27), ((70, 230), 1 << 27), ((n,), 64 * 320 * spec["mixer"]["left"]["heads"])):
+            monkeypatch.setattr(TalkingAttention, "DENSE_FROM", 128)
+            monkeypatch.setattr(TalkingAttention, "DENSE_SCORES", most)
+            h = Harness(folder, torch.bfloat16, max_len=320)
+            got = run_part(h, h.model.layers[layer].mixer, x, torch.bfloat16, sizes, entry=entry)
+            assert any(k[0] == "talk_s" for k in h.runner.buffers._flat), "the tensor-core form did not run"
+            assert part_err(got, want) < PART_TOL[torch.bfloat16], (name, sizes)
+            assert part_err(got, cores) < PART_TOL[torch.bfloat16], (name, sizes)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_feed_forwards_alone(tmp_path, dtype):
     g = torch.Generator().manual_seed(6)
