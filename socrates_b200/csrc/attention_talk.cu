@@ -280,8 +280,8 @@ __global__ void __launch_bounds__(THREADS) talk_attention_kernel(TalkArgs a) {
 // The same attention for ONE long prompt portion in the bfloat16 engine, with both products on the tensor
 // cores through the engine's matrix product: the portion's keys are gathered out of their pages into one
 // matrix per KV head (values transposed, twice side by side), the raw scores of a block of queries are one
-// product per KV head (float32 sums over the bfloat16 q and k), a kernel mixes them across the heads, masks,
-// takes the softmax in float32 and writes every weight as two bfloat16 terms [high | low], and the weighted
+// product per KV head (float32 sums over the bfloat16 q and k), a kernel mixes them across the heads in place,
+// another masks, takes the softmax in float32 and writes every weight as two bfloat16 terms [high | low], and the weighted
 // values are one more product per KV head over both terms.  The kernels here are the three steps between
 // the products.
 struct TalkDenseArgs {
@@ -342,25 +342,50 @@ __global__ void __launch_bounds__(256) talk_gather_q_kernel(TalkDenseArgs a) {
     }
 }
 
-// one (query, head): mix the raw scores of all heads, mask, softmax, two bfloat16 terms a weight
+// every head's scaled score from all heads' raw scores of the same (query, key), IN PLACE: a thread owns one
+// (query, key), reads its HB raw scores once and writes the mixed ones over them
+template <int HB>
+__global__ void __launch_bounds__(256) talk_mix_kernel(TalkDenseArgs a, float* S) {
+    sb::pdl_launch_dependents();
+    __shared__ float tw[HB * HB];
+    const int i = blockIdx.x, H = a.H, G = H / a.Hkv, Cp = a.Cp;
+    for (int c = threadIdx.x; c < HB * HB; c += blockDim.x) {
+        const int h = c / HB, g = c - h * HB;
+        tw[c] = (h < H && g < H) ? a.talk[h * H + g] * a.scale : 0.f;
+    }
+    sb::pdl_wait();
+    __syncthreads();
+    const int j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j >= Cp || j > a.pos0 + i) return;              // keys behind the query are never read
+    float raw[HB];
+#pragma unroll
+    for (int g = 0; g < HB; ++g) {
+        const int kh = g / G, gg = g - kh * G;
+        raw[g] = g < H ? S[((size_t)kh * G * a.nb + (size_t)gg * a.nb + i) * Cp + j] : 0.f;
+    }
+    for (int h = 0; h < H; ++h) {
+        float m = 0.f;
+#pragma unroll
+        for (int g = 0; g < HB; ++g) m = fmaf(tw[h * HB + g], raw[g], m);
+        const int kh = h / G, gg = h - kh * G;
+        S[((size_t)kh * G * a.nb + (size_t)gg * a.nb + i) * Cp + j] = m;
+    }
+}
+
+// one (query, head): mask the mixed scores, softmax, two bfloat16 terms a weight
 __global__ void __launch_bounds__(256) talk_mix_softmax_kernel(TalkDenseArgs a) {
     sb::pdl_launch_dependents();
     extern __shared__ float row[];              // Cp mixed scores
-    __shared__ float scratch[33], tw[64];
+    __shared__ float scratch[33];
     const int i = blockIdx.x, h = blockIdx.y, H = a.H, G = H / a.Hkv, Cp = a.Cp;
-    for (int g = threadIdx.x; g < H; g += blockDim.x) tw[g] = a.talk[h * H + g] * a.scale;
     sb::pdl_wait();
-    __syncthreads();
     const int pos = a.pos0 + i;
     const int lo = (a.window > 0 && pos + 1 > a.window) ? pos + 1 - a.window : 0;
     const int hi = min(pos, a.C - 1);           // keys lo .. hi are seen
     float mx = -INFINITY;
+    const float* mixed = a.S + ((size_t)(h / G) * G * a.nb + (size_t)(h % G) * a.nb + i) * Cp;
     for (int j = lo + threadIdx.x; j <= hi; j += blockDim.x) {
-        float s = 0.f;
-        for (int g = 0; g < H; ++g) {
-            const int kh = g / G, gg = g - kh * G;
-            s = fmaf(tw[g], a.S[((size_t)kh * G * a.nb + (size_t)gg * a.nb + i) * Cp + j], s);
-        }
+        const float s = mixed[j];
         row[j] = s;
         mx = fmaxf(mx, s);
     }
@@ -379,6 +404,7 @@ __global__ void __launch_bounds__(256) talk_mix_softmax_kernel(TalkDenseArgs a) 
     }
     const float inv = 1.0f / block_sum(sum, scratch);
     const int kh = h / G, gg = h - kh * G;
+    (void)H;
     __nv_bfloat16* pr = a.P + ((size_t)kh * G * a.nb + (size_t)gg * a.nb + i) * 2 * Cp;
     for (int j = threadIdx.x; j < Cp; j += blockDim.x) {
         float p = (j >= lo && j <= hi) ? row[j] * inv : 0.f;
@@ -510,6 +536,12 @@ extern "C" int sb_attention_talk_dense(int step, const void* q, const void* k_po
             cudaFuncSetAttribute(talk_mix_softmax_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             once.flag() = true;
         }
+        float* mixed = const_cast<float*>(S);
+        const dim3 mgrid(nb, (Cp + 255) / 256);
+        if (H <= 8) sb::launch(talk_mix_kernel<8>, mgrid, dim3(256), 0, stream, a, mixed);
+        else if (H <= 16) sb::launch(talk_mix_kernel<16>, mgrid, dim3(256), 0, stream, a, mixed);
+        else if (H <= 32) sb::launch(talk_mix_kernel<32>, mgrid, dim3(256), 0, stream, a, mixed);
+        else sb::launch(talk_mix_kernel<64>, mgrid, dim3(256), 0, stream, a, mixed);
         sb::launch(talk_mix_softmax_kernel, dim3(nb, H), dim3(256), smem, stream, a);
     } else {
         sb::launch(talk_finish_kernel, dim3(nb), dim3(256), 0, stream, a);
